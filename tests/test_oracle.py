@@ -1,0 +1,104 @@
+"""The CPU oracle against the reference's own test-side functions (golden vectors made from the reference test source
+by tests/golden/make_golden.py) and against torch's FP8 dtypes."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import decode_gemv_oracle as oc
+from oracle import workloads as wl
+
+
+def test_e2m1_table_is_the_references(golden):
+    assert np.array_equal(oc.E2M1_TABLE, golden["e2m1_table"])
+    assert np.array_equal(np.signbit(oc.E2M1_TABLE), np.signbit(golden["e2m1_table"]))
+
+
+def test_e4m3_decode_matches_every_byte(golden):
+    mine = oc.e4m3_to_float(np.arange(256, dtype=np.uint8))
+    want = golden["e4m3_all"]
+    assert np.array_equal(np.isnan(mine), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(mine[ok], want[ok])
+    # and torch's cast today agrees with the stored table
+    now = torch.arange(256, dtype=torch.uint8).view(torch.float8_e4m3fn).double().numpy()
+    assert np.array_equal(now[ok], want[ok])
+
+
+def test_e8m0_decode():
+    e = np.arange(256, dtype=np.uint8)
+    v = oc.e8m0_to_float(e)
+    assert v[0] == 2.0 ** -127 and v[127] == 1.0 and v[254] == 2.0 ** 127 and np.isnan(v[255])
+    if hasattr(torch, "float8_e8m0fnu"):
+        t = torch.from_numpy(e[:255].copy()).view(torch.float8_e8m0fnu).double().numpy()
+        assert np.array_equal(t, v[:255])
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_nvfp4_values_and_product(golden, tag):
+    c, s, i = (golden[f"nvfp4_{tag}_{p}"] for p in ("codes", "scales", "inverse"))
+    v = oc.nvfp4_values(c, s, i)
+    assert np.array_equal(v, golden[f"nvfp4_{tag}_values"])
+    x = torch.from_numpy(golden[f"nvfp4_{tag}_x"])
+    assert np.array_equal(oc.gemv_exact(x, v).numpy(), golden[f"nvfp4_{tag}_exact"])
+    assert np.array_equal(oc.to_blocked(s), golden[f"nvfp4_{tag}_blocked"])
+    n, k = c.shape[0], c.shape[1] * 2
+    assert oc.to_blocked(s).size == oc.blocked_numel(n, k)
+    assert np.array_equal(oc.from_blocked(oc.to_blocked(s), n, k // 16), s)
+
+
+@pytest.mark.parametrize("tag", ["row", "mx"])
+def test_fp8_values_and_product(golden, tag):
+    c, s = golden[f"fp8_{tag}_codes"], golden[f"fp8_{tag}_scales"]
+    v = oc.fp8_values(c, s)
+    assert np.array_equal(v, golden[f"fp8_{tag}_values"])
+    x = torch.from_numpy(golden[f"fp8_{tag}_x"])
+    assert np.array_equal(oc.gemv_exact(x, v).numpy(), golden[f"fp8_{tag}_exact"])
+
+
+def test_bf16_product(golden):
+    w = torch.from_numpy(golden["bf16_w"]).to(torch.bfloat16)
+    x = torch.from_numpy(golden["bf16_x"])
+    assert np.array_equal(oc.gemv_exact(x, oc.bf16_values(w)).numpy(), golden["bf16_exact"])
+
+
+def test_generators_reproduce_the_golden_inputs(golden):
+    c, s, i = wl.ref_nvfp4(96, 256)
+    assert np.array_equal(c.numpy(), golden["nvfp4_a_codes"]) and np.array_equal(s.numpy(), golden["nvfp4_a_scales"])
+    assert np.array_equal(i.numpy(), golden["nvfp4_a_inverse"])
+    fc, fs = wl.ref_fp8(70, 512, True)
+    assert np.array_equal(fc.numpy(), golden["fp8_mx_codes"]) and np.array_equal(fs.numpy(), golden["fp8_mx_scales"])
+    assert np.array_equal(wl.activations(16, 256).float().numpy(), golden["nvfp4_a_x"])
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "fp8", "mxfp8", "bf16"])
+def test_fp32_dequant_baseline_agrees_with_the_fp64_values(fmt):
+    n, k, m = 48, 512, 4
+    tensors = {"nvfp4": wl.cfg_nvfp4, "fp8": wl.cfg_fp8, "mxfp8": wl.cfg_mxfp8}.get(fmt, None)
+    tensors = tensors(n, k) if tensors else (wl.cfg_bf16(n, k),)
+    x = wl.activations(m, k)
+    v = oc.values_of(fmt, tensors)
+    deq = oc.dequant_fp32(fmt, tensors)
+    if fmt == "fp8":      # code * FP32 row scale rounds once in FP32
+        assert np.allclose(deq.double().numpy(), v, rtol=1e-7, atol=0)
+    else:                 # code * block scale (* inverse 1.0) is exact in FP32
+        assert np.array_equal(deq.double().numpy(), v)
+    out = oc.gemv_fp32(x, deq, torch.float32)
+    assert oc.within_fp32_bound(out, x, v)
+    assert oc.max_rel_error(oc.gemv_fp32(x, deq), oc.gemv_exact(x, v)) < 1e-2
+
+
+def test_mxfp8_generator_follows_the_shared_exponent_rule():
+    c, e = wl.cfg_mxfp8(8, 256)
+    v = oc.e4m3_to_float(c.numpy()).reshape(8, -1, 32)
+    assert not np.isnan(v).any()
+    amax = np.abs(v).max(axis=-1)
+    assert (amax >= 256).all() and (amax <= 448).all()      # block max scaled into [256, 512), saturated at 448
+    assert e.min() > 90 and e.max() < 130
+
+
+def test_weight_bytes_of_the_configurations():
+    assert wl.weight_bytes("nvfp4", 4096, 4096) == 9_453_568
+    assert wl.weight_bytes("fp8", 28672, 8192) == 234_995_712
+    assert wl.weight_bytes("mxfp8", 13824, 5120) == 72_990_720
+    assert wl.weight_bytes("bf16", 8192, 8192) == 134_217_728
+    assert sum(wl.weight_bytes("nvfp4", n, k) for _, k, n in wl.STACK_ROLES) == 481_632_256

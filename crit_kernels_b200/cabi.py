@@ -1,0 +1,50 @@
+"""ctypes view of the C ABI (include/decode_gemv_b200.h), for tests, benches and callers without torch ops.
+
+Loads lib/libdecode_gemv_b200.so; there is no fallback when it is missing."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libdecode_gemv_b200.so")
+
+_p, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)
+SIGNATURES = {
+    "dg_enqueue_nvfp4": (_i, [_p, _i, _i, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dg_enqueue_fp8": (_i, [_p, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dg_enqueue_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dg_hardware_decode": (_i, []),
+    "dg_plan": (_i, [_i, _i, _i, _i, _f]),
+    "dg_take_status": (_i, []),
+    "dg_version": (_i, []),
+}
+FMT = {"bf16": 0, "fp8": 1, "mxfp8": 2, "nvfp4": 3}
+_lib = None
+
+
+def library_path() -> str:
+    return _PATH
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library with argument types set; raises OSError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_PATH):
+            raise OSError(f"{_PATH} is missing: build it with `python -m crit_kernels_b200.build`")
+        lib = ctypes.CDLL(_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def plan(fmt: str, m: int, n: int, k: int) -> dict:
+    """The launch shape a call of these sizes gets (host only)."""
+    out = (ctypes.c_int * 6)()
+    code = load().dg_plan(FMT[fmt], m, n, k, out)
+    if code:
+        raise ValueError(f"dg_plan refused fmt={fmt} M={m} N={n} K={k} (cudaError {code})")
+    keys = ("ctas", "rows_per_warp", "steps", "stages", "stage_bytes", "smem_bytes")
+    return dict(zip(keys, out))

@@ -1,0 +1,199 @@
+// C ABI of the B200 decode GEMVs (include/decode_gemv_b200.h): argument validation, launch planning, dispatch.
+//
+// Mirrors the reference's raw CUDA API (decode-gemv/decode_gemv_cuda/decode_gemv.cu:378-427): the same refusals
+// (cudaErrorInvalidValue for M outside 1..16, N < 1, K not a multiple the format needs, both or neither FP8 scale),
+// cudaGetLastError() after the launch, no allocation and no host synchronisation on the enqueue path.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "../../include/decode_gemv_b200.h"
+#include "dg_kernel.cuh"
+#include "dg_tables.h"
+
+namespace {
+
+using dg::Params;
+
+// Error word the kernels' bounded waits report into: one per device that loads the library.
+__device__ int dg_status_word;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+  std::atomic<int> ready{0};   // 0 unknown, 1 initialised, -1 unusable
+  int sms = 0;
+  int* status = nullptr;
+};
+DeviceState g_devices[kMaxDevices];
+
+const void* const* const kTables[] = {dg_table_bf16,       dg_table_fp8_bf16,   dg_table_fp8_f16,  dg_table_mxfp8_bf16,
+                                      dg_table_mxfp8_f16,  dg_table_nvfp4_bf16, dg_table_nvfp4_f16};
+
+// Per device, once: SM count, the address of the status word, and the opt-in to 227 KB of dynamic shared memory for
+// every kernel. None of this is a stream operation. Returns nullptr when the device cannot run sm_100a code.
+DeviceState* device_state() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  DeviceState& st = g_devices[dev];
+  int ready = st.ready.load(std::memory_order_acquire);
+  if (ready == 1) return &st;
+  if (ready == -1) return nullptr;
+  int major = 0, sms = 0;
+  void* status = nullptr;
+  bool ok = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess && major == 10 &&
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0 &&
+            cudaGetSymbolAddress(&status, dg_status_word) == cudaSuccess;
+  for (const void* const* table : kTables)
+    for (int m = 0; ok && m < 16; ++m)
+      ok = cudaFuncSetAttribute(table[m], cudaFuncAttributeMaxDynamicSharedMemorySize, dg::kSmemLimit) == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    st.ready.store(-1, std::memory_order_release);
+    return nullptr;
+  }
+  st.sms = sms;
+  st.status = static_cast<int*>(status);
+  st.ready.store(1, std::memory_order_release);
+  return &st;
+}
+
+struct FormatInfo {
+  int e, scb;   // elements per 16-byte block, scale bytes per 512-byte step
+};
+constexpr FormatInfo kFormats[4] = {{8, 0}, {16, 0}, {16, 16}, {32, 64}};
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Launch shape: a speed choice from (format, M, N, K, SM count) only; no row's bits depend on it.
+//   CTAs            one per SM, fewer when the matrix has under one row per consumer warp and SM
+//   rows per warp   the most the kernel holds (rows_max), less when a CTA's range is short
+//   steps           512-byte steps per ring stage: about 24 KB of weights per stage, activations under 32 KB
+//   stages          as many as fit in shared memory, at most kMaxStages
+bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem) {
+  const FormatInfo f = kFormats[fmt];
+  const long long row_bits = (long long)K * 128 / f.e;   // 16 bytes per e elements
+  p.row_bytes = (int)(row_bits / 8);
+  p.nblk = p.row_bytes / 16;
+  ctas = sms < ceil_div(N, dg::kConsumerWarps) ? sms : ceil_div(N, dg::kConsumerWarps);
+  const int rows_per_cta = ceil_div(N, ctas);
+  const int per_warp = ceil_div(rows_per_cta, dg::kConsumerWarps);
+  const int rmax = dg::rows_max(fmt, M);
+  p.rows_per_warp = per_warp < rmax ? per_warp : rmax;
+  const int rows_cap = dg::kConsumerWarps * p.rows_per_warp;
+  const int w_step = rows_cap * (dg::kStepBytes + f.scb);
+  const int x_step = M * 64 * f.e;
+  const int row_steps = ceil_div(p.nblk, 32);
+  int steps = ceil_div(24576, w_step);
+  if (steps > row_steps) steps = row_steps;
+  if (steps > 8) steps = 8;
+  while (steps > 1 && steps * x_step > 32768) --steps;
+  if (steps < 1) steps = 1;
+  p.steps = steps;
+  p.stage_bytes = (steps * (w_step + x_step) + 127) & ~127;
+  int stages = (dg::kSmemLimit - dg::kSmemHeader) / p.stage_bytes;
+  if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+  if (stages < 2) return false;
+  p.stages = stages;
+  smem = dg::kSmemHeader + stages * p.stage_bytes;
+  return true;
+}
+
+bool aligned(const void* ptr, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(ptr) % bytes == 0; }
+
+int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
+  DeviceState* st = device_state();
+  if (!st) return (int)cudaErrorInvalidDevice;
+  int ctas = 0, smem = 0;
+  if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
+  p.status = st->status;
+  void* args[] = {&p};
+  const cudaError_t e = cudaLaunchKernel(kTables[table][M - 1], dim3(ctas), dim3(dg::kThreads), args, smem, stream);
+  return (int)(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+}  // namespace
+
+extern "C" {
+
+int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales, int blocked,
+                     const float* inverse, void* out, int ldo, int out_kind, int M, int N, int K, void* stream) {
+  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return (int)cudaErrorInvalidValue;
+  if (!x || !codes || !scales || !inverse || !out || ldx % 8 || !aligned(x, 16) || !aligned(codes, 16) ||
+      !aligned(scales, 2) || !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1))
+    return (int)cudaErrorInvalidValue;
+  Params p{};
+  p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse; p.out = out; p.ldo = ldo;
+  p.out_kind = out_kind == 0 ? dg::OUT_F32 : (x_is_bf16 ? dg::OUT_BF16 : dg::OUT_F16);
+  p.N = N; p.K = K;
+  p.scale_row_bytes = K / 16;
+  p.ct = blocked ? (K / 16 + 3) / 4 : 0;
+  // Scale rows travel by bulk copy when every window of every row starts on 16 bytes and is a multiple of 16 bytes
+  // long (K a multiple of 256, base on 16 bytes); otherwise, and for the tiled layout, lanes read them directly.
+  p.scale_mode = blocked ? dg::SCALES_BLOCKED
+                         : (K % 256 == 0 && aligned(scales, 16)) ? dg::SCALES_STAGED : dg::SCALES_DIRECT;
+  return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
+}
+
+int dg_enqueue_fp8(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const float* row_scale,
+                   const uint8_t* mx_scale, void* out, int ldo, int out_kind, int M, int N, int K, void* stream) {
+  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 16 || K % 16 || (mx_scale && K % 32) || (!row_scale == !mx_scale))
+    return (int)cudaErrorInvalidValue;
+  if (!x || !codes || !out || ldx % 8 || !aligned(x, 16) || !aligned(codes, 16) || !aligned(row_scale, 4) ||
+      (out_kind != 0 && out_kind != 1))
+    return (int)cudaErrorInvalidValue;
+  Params p{};
+  p.x = x; p.ldx = ldx; p.w = codes; p.scales = mx_scale; p.row_scale = row_scale; p.out = out; p.ldo = ldo;
+  p.out_kind = out_kind == 0 ? dg::OUT_F32 : (x_is_bf16 ? dg::OUT_BF16 : dg::OUT_F16);
+  p.N = N; p.K = K;
+  p.scale_row_bytes = K / 32;
+  p.scale_mode = !mx_scale ? dg::SCALES_NONE
+                           : (K % 512 == 0 && aligned(mx_scale, 16)) ? dg::SCALES_STAGED : dg::SCALES_DIRECT;
+  const int fmt = mx_scale ? dg::FMT_MXFP8 : dg::FMT_FP8;
+  return launch((mx_scale ? 3 : 1) + (x_is_bf16 ? 0 : 1), fmt, p, M, static_cast<cudaStream_t>(stream));
+}
+
+int dg_enqueue_bf16(const void* x, int ldx, const void* w, void* out, int ldo, int out_kind, int M, int N, int K,
+                    void* stream) {
+  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 8 || K % 8) return (int)cudaErrorInvalidValue;
+  if (!x || !w || !out || ldx % 8 || !aligned(x, 16) || !aligned(w, 16) || (out_kind != 0 && out_kind != 1))
+    return (int)cudaErrorInvalidValue;
+  Params p{};
+  p.x = x; p.ldx = ldx; p.w = static_cast<const uint8_t*>(w); p.out = out; p.ldo = ldo;
+  p.out_kind = out_kind == 0 ? dg::OUT_F32 : dg::OUT_BF16;
+  p.N = N; p.K = K;
+  p.scale_mode = dg::SCALES_NONE;
+  return launch(0, dg::FMT_BF16, p, M, static_cast<cudaStream_t>(stream));
+}
+
+int dg_hardware_decode(void) { return device_state() ? 1 : -1; }
+
+int dg_plan(int fmt, int M, int N, int K, int plan[6]) {
+  static const int kmult[4] = {8, 16, 32, 32};
+  if (fmt < 0 || fmt > 3 || M < 1 || M > DG_MAX_ROWS || N < 1 || K < kmult[fmt] || K % kmult[fmt] || !plan)
+    return (int)cudaErrorInvalidValue;
+  int sms = 148;
+  if (DeviceState* st = device_state()) sms = st->sms;
+  Params p{};
+  p.N = N; p.K = K;
+  int ctas = 0, smem = 0;
+  if (!make_plan(fmt, M, N, K, sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
+  plan[0] = ctas; plan[1] = p.rows_per_warp; plan[2] = p.steps; plan[3] = p.stages; plan[4] = p.stage_bytes;
+  plan[5] = smem;
+  return 0;
+}
+
+int dg_take_status(void) {
+  DeviceState* st = device_state();
+  if (!st) return -(int)cudaErrorInvalidDevice;
+  int word = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && word) e = cudaMemset(st->status, 0, sizeof(int));
+  return e == cudaSuccess ? word : -(int)e;
+}
+
+int dg_version(void) { return 100; }
+
+}  // extern "C"

@@ -1,0 +1,534 @@
+// Weight-only decode GEMV for B200 (sm_100a): out[m][n] = scale[n] * sum_k x[m][k] * w[n][k] for 1..16 activation
+// rows, weights stored as BF16, FP8 E4M3 (row scale), MXFP8 (E8M0 per 32) or NVFP4 (E2M1 codes, E4M3 per 16).
+//
+// Replaces the kernels of the reference package decode-gemv (decode_gemv_cuda/decode_gemv.cu:85 gemv_kernel,
+// :191 bf16_kernel, :285 fp8_kernel). Same formats, same contract (FP32 sums whose order never depends on the row
+// count), a different machine mapping:
+//
+//   * one persistent CTA per SM: 7 consumer warps + 1 producer warp. The matrix rows are split into one contiguous
+//     range per CTA; a range is walked in tiles of 7*r rows (r rows per consumer warp) and each tile in K windows.
+//   * the producer warp streams every window of a tile into a shared-memory ring: one cp.async.bulk (TMA 1-D bulk
+//     copy, mbarrier complete_tx) per weight row (and per row of block scales), issued by 32 lanes in parallel, plus
+//     the matching window of the activations as 16-byte cp.async copies into a bank-swizzled layout. Bytes in flight
+//     are set by the ring (up to ~200 KB per SM), not by registers.
+//   * consumer warp w owns rows w, w+7, ... of the tile. Lane l owns the 16-byte blocks l, l+32, ... of each row and
+//     keeps two FP32 chains per (row, m): even and odd elements, advanced together by one packed fma.rn.f32x2. The
+//     chains visit the blocks in ascending order, the two chains are added, and one xor-shuffle tree (16, 8, 4, 2, 1)
+//     adds the lanes; the row scale multiplies once and the result is rounded once to the output type.
+//
+// A row's summation order is therefore a function of K and the format alone: it does not depend on M, on the rows a
+// warp holds, on the tile or window sizes the launch picked, on the CTA count, or on which slice of the matrix a
+// device holds. Every product is exact in FP32 (weights and block scales have few significant bits), NVFP4 block
+// scales multiply a 16-element partial sum (one fma per block and row instead of one multiply per weight).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace dg {
+
+enum : int { FMT_BF16 = 0, FMT_FP8 = 1, FMT_MXFP8 = 2, FMT_NVFP4 = 3 };
+enum : int { SCALES_NONE = 0, SCALES_STAGED = 1, SCALES_DIRECT = 2, SCALES_BLOCKED = 3 };
+enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2 };
+
+constexpr int kConsumerWarps = 7;   // + 1 producer = 8 warps: two per SM sub-partition, 255 registers each
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMaxStages = 12;
+constexpr int kStepBytes = 512;            // 32 lanes x 16 bytes of one weight row
+constexpr int kSmemHeader = 256;           // mbarriers + abort flag
+constexpr int kSmemLimit = 232448;         // 227 KB of dynamic shared memory per CTA on sm_100
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // bounded waits: after 2 s give up, flag it, leave
+
+// status word bits written on a wait that ran out (never expected; the host can read the word)
+constexpr int kStatusProducerTimeout = 1;
+constexpr int kStatusConsumerTimeout = 2;
+
+template <int FMT> struct Format;
+template <> struct Format<FMT_BF16>  { static constexpr int E = 8,  SCB = 0;  };   // elements / scale bytes per
+template <> struct Format<FMT_FP8>   { static constexpr int E = 16, SCB = 0;  };   // 16-byte block and per 512-byte
+template <> struct Format<FMT_MXFP8> { static constexpr int E = 16, SCB = 16; };   // step of one row
+template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
+
+// Rows a consumer warp may hold at once (a register-budget choice; never changes a row's bits).
+__host__ __device__ constexpr int rows_max(int fmt, int m) {
+  return fmt == FMT_NVFP4 ? (m <= 8 ? 4 : 2) : (m <= 4 ? 8 : 4);
+}
+
+struct Params {
+  const void* x;             // [M][ldx] BF16 or FP16
+  const uint8_t* w;          // weight rows, row_bytes apart
+  const uint8_t* scales;     // NVFP4 E4M3 [N][K/16] (or tiled), MXFP8 E8M0 [N][K/32]; else null
+  const float* row_scale;    // FP8 row scale / NVFP4 inverse global scale [N]; else null
+  void* out;                 // [M][ldo]
+  int* status;               // device word for kStatus* bits
+  int ldx, ldo, out_kind;
+  int N, K;
+  int row_bytes;             // bytes of one weight row
+  int nblk;                  // 16-byte blocks per row
+  int scale_row_bytes;       // bytes of one row-major scale row
+  int scale_mode;            // SCALES_*
+  int ct;                    // tiled scales: 4-block tiles per tile row
+  int steps;                 // 512-byte steps per ring stage
+  int stages;                // ring depth
+  int rows_per_warp;         // r: a full tile is kConsumerWarps * r rows
+  int stage_bytes;           // bytes of one ring stage
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// PTX wrappers: mbarrier, 1-D bulk copy (TMA), 16-byte cp.async tied to an mbarrier.
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. False when it gave up or another thread of the CTA already had: the caller leaves its loops.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const unsigned long long start = global_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_ns() - start > kWaitLimitNs) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Element conversions. All exact.
+
+__device__ __forceinline__ float2 pair_to_f32(uint32_t v, __nv_bfloat16) {   // two BF16 -> two FP32
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+__device__ __forceinline__ float2 pair_to_f32(uint32_t v, __half) {          // two FP16 -> two FP32
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+__device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t v) {                // low 16 bits: two E4M3 -> two FP32
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+__device__ __forceinline__ float2 e2m1x2_to_f32(uint32_t v) {                // low 8 bits: two E2M1 -> two FP32
+  const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)v, __NV_E2M1);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+// E8M0 exponent byte as FP32 2^(e-127); e = 0 is the FP32 subnormal 2^-127 and e = 255 is NaN, as the reference
+// decodes them (decode_gemv.cu:275-278).
+__device__ __forceinline__ float e8m0_to_f32(uint32_t e) {
+  return __uint_as_float(e == 0u ? 0x00400000u : e == 255u ? 0x7fc00000u : e << 23);
+}
+// Offset of the byte of 16-block j (j even) of row n in cuBLASLt's 128 x 4 tiled scale layout, ct tiles per tile
+// row: the layout the reference reads at decode_gemv.cu:78-82.
+__device__ __forceinline__ size_t tiled_scale_offset(int n, int j, int ct) {
+  const int r = n & 127;
+  return ((size_t)(n >> 7) * ct + (j >> 2)) * 512 + (size_t)(r & 31) * 16 + (r >> 5) * 4 + (j & 3);
+}
+
+__device__ __forceinline__ void store_out(void* out, int kind, size_t idx, float v) {
+  if (kind == OUT_F32) reinterpret_cast<float*>(out)[idx] = v;
+  else if (kind == OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tile walk shared by producer and consumers: CTA c owns rows [lo, hi); tiles of kConsumerWarps * r rows, the last one shorter.
+
+struct Walk {
+  int lo, hi, tile_rows, ntiles, nwin, win_bytes;
+  __device__ __forceinline__ Walk(const Params& p) {
+    lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
+    hi = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
+    tile_rows = kConsumerWarps * p.rows_per_warp;
+    ntiles = (hi - lo + tile_rows - 1) / tile_rows;
+    win_bytes = p.steps * kStepBytes;
+    nwin = (p.row_bytes + win_bytes - 1) / win_bytes;
+  }
+};
+
+// Shared-memory stage: [weights rows_cap x win_bytes][scales rows_cap x steps*SCB][x M x steps*64*E bytes].
+template <int FMT, int M>
+struct StageLayout {
+  static constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB;
+  int w_row, sc_row, x_row, sc_off, x_off;
+  __device__ __forceinline__ StageLayout(const Params& p) {
+    const int rows_cap = kConsumerWarps * p.rows_per_warp;
+    w_row = p.steps * kStepBytes;
+    sc_row = p.steps * SCB;
+    x_row = p.steps * 64 * E;
+    sc_off = rows_cap * w_row;
+    x_off = sc_off + rows_cap * sc_row;
+  }
+};
+
+// 16-byte slot s of an activation row lands at slot s ^ ((s >> 3) & (NQ - 1)) (NQ = 16-byte slots a lane reads per
+// block): the eight lanes of a quarter warp then read eight different bank groups.
+template <int NQ>
+__device__ __forceinline__ int swizzle_slot(int s) { return s ^ ((s >> 3) & (NQ - 1)); }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Producer warp.
+
+template <int FMT, int M>
+__device__ __forceinline__ void producer(const Params& p, unsigned char* smem, uint32_t full0, uint32_t empty0,
+                                         volatile int* abort_flag) {
+  constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
+  const int lane = threadIdx.x & 31;
+  const Walk wk(p);
+  const StageLayout<FMT, M> lay(p);
+  const uint32_t ring = smem_addr(smem) + kSmemHeader;
+  const bool staged = SCB != 0 && p.scale_mode == SCALES_STAGED;
+  const unsigned char* xg = reinterpret_cast<const unsigned char*>(p.x);
+  int s = 0;
+  uint32_t parity = 0;
+  for (int t = 0; t < wk.ntiles; ++t) {
+    const int row0 = wk.lo + t * wk.tile_rows;
+    const int rows = min(wk.tile_rows, wk.hi - row0);
+    for (int win = 0; win < wk.nwin; ++win) {
+      const uint32_t full = full0 + 8u * s, empty = empty0 + 8u * s;
+      if (!mbar_wait(empty, parity ^ 1u, abort_flag)) {
+        if (lane == 0 && p.status) atomicOr(p.status, kStatusProducerTimeout);
+        return;
+      }
+      const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
+      const int byte0 = win * wk.win_bytes;
+      const int wbytes = min(wk.win_bytes, p.row_bytes - byte0);
+      // activations of this window: wbytes / 16 blocks of E elements per row, 16 bytes (8 elements) per copy
+      const int slots = (wbytes >> 4) * NQ;
+      const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
+      for (int c = lane; c < M * slots; c += 32) {
+        const int m = c / slots, sl = c - m * slots;
+        cp_async16(stage + lay.x_off + m * lay.x_row + swizzle_slot<NQ>(sl) * 16,
+                   xg + (size_t)m * p.ldx * 2 + xbyte0 + (size_t)sl * 16);
+      }
+      cp_async_arrive_noinc(full);
+      const int scbytes = staged ? (wbytes >> 9) * SCB + (((wbytes & 511) * SCB) >> 9) : 0;
+      if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)rows * (uint32_t)(wbytes + scbytes));
+      __syncwarp();
+      for (int r = lane; r < rows; r += 32) {
+        const size_t n = (size_t)(row0 + r);
+        bulk_g2s(stage + r * lay.w_row, p.w + n * p.row_bytes + byte0, (uint32_t)wbytes, full);
+        if (staged)
+          bulk_g2s(stage + lay.sc_off + r * lay.sc_row, p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row,
+                   (uint32_t)scbytes, full);
+      }
+      if (++s == p.stages) { s = 0; parity ^= 1u; }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Consumer bodies: one 16-byte block of each of R rows times M activation rows. `wrow` points at the block of the
+// warp's first row in the stage, rows are `wstride` bytes apart; `xs` at the stage's activations.
+// acc[r][m] = (even chain, odd chain).
+
+template <int NQ>
+struct XOffsets {   // byte offsets of the lane's NQ swizzled slots inside one step of one activation row
+  int off[NQ];
+  __device__ __forceinline__ XOffsets(int lane) {
+#pragma unroll
+    for (int j = 0; j < NQ; ++j) off[j] = swizzle_slot<NQ>(lane * NQ + j) * 16;
+  }
+};
+
+template <int M, int R, typename XT>
+__device__ __forceinline__ void body_bf16(const unsigned char* wrow, int wstride, int nr, const unsigned char* xs,
+                                          int x_row, float2 (&acc)[R][M]) {
+  float2 wf[R][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint4 v = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+    wf[r][0] = pair_to_f32(v.x, __nv_bfloat16());
+    wf[r][1] = pair_to_f32(v.y, __nv_bfloat16());
+    wf[r][2] = pair_to_f32(v.z, __nv_bfloat16());
+    wf[r][3] = pair_to_f32(v.w, __nv_bfloat16());
+  }
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const uint4 v = *reinterpret_cast<const uint4*>(xs + m * x_row);
+    const float2 x0 = pair_to_f32(v.x, XT()), x1 = pair_to_f32(v.y, XT()), x2 = pair_to_f32(v.z, XT()),
+                 x3 = pair_to_f32(v.w, XT());
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float2 a = acc[r][m];
+      a = __ffma2_rn(wf[r][0], x0, a);
+      a = __ffma2_rn(wf[r][1], x1, a);
+      a = __ffma2_rn(wf[r][2], x2, a);
+      a = __ffma2_rn(wf[r][3], x3, a);
+      acc[r][m] = a;
+    }
+  }
+}
+
+// FP8 / MXFP8: the block is two sub-blocks of 8 weights (words 0-1, words 2-3). `sc` holds the MXFP8 scale of each
+// row's block (unused for FP8).
+template <bool MX, int M, int R, typename XT>
+__device__ __forceinline__ void body_fp8(const unsigned char* wrow, int wstride, int nr, const float (&sc)[R],
+                                         const unsigned char* xs, int x_row, const XOffsets<2>& xo,
+                                         float2 (&acc)[R][M]) {
+  uint4 wv[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    float2 wf[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t a = j ? wv[r].z : wv[r].x, b = j ? wv[r].w : wv[r].y;
+      wf[r][0] = e4m3x2_to_f32(a);
+      wf[r][1] = e4m3x2_to_f32(a >> 16);
+      wf[r][2] = e4m3x2_to_f32(b);
+      wf[r][3] = e4m3x2_to_f32(b >> 16);
+      if (MX) {
+        const float2 s2 = make_float2(sc[r], sc[r]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) wf[r][q] = __fmul2_rn(wf[r][q], s2);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint4 v = *reinterpret_cast<const uint4*>(xs + m * x_row + xo.off[j]);
+      const float2 x0 = pair_to_f32(v.x, XT()), x1 = pair_to_f32(v.y, XT()), x2 = pair_to_f32(v.z, XT()),
+                   x3 = pair_to_f32(v.w, XT());
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float2 a = acc[r][m];
+        a = __ffma2_rn(wf[r][0], x0, a);
+        a = __ffma2_rn(wf[r][1], x1, a);
+        a = __ffma2_rn(wf[r][2], x2, a);
+        a = __ffma2_rn(wf[r][3], x3, a);
+        acc[r][m] = a;
+      }
+    }
+  }
+}
+
+// NVFP4: the block is 32 codes = two scale blocks of 16 (words 0-1 with scale .x, words 2-3 with scale .y). The 16
+// products of a scale block are summed first (two chains of 8), then acc = fma(scale, partial, acc).
+template <int M, int R, typename XT>
+__device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, int wstride, int nr, const float2 (&sc)[R],
+                                           const unsigned char* xs, int x_row, const XOffsets<4>& xo,
+                                           float2 (&acc)[R][M]) {
+  uint4 wv[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float2 wf[R][8];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t a = h ? wv[r].z : wv[r].x, b = h ? wv[r].w : wv[r].y;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        wf[r][q] = e2m1x2_to_f32(a >> (8 * q));
+        wf[r][4 + q] = e2m1x2_to_f32(b >> (8 * q));
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint4 u = *reinterpret_cast<const uint4*>(xs + m * x_row + xo.off[2 * h]);
+      const uint4 v = *reinterpret_cast<const uint4*>(xs + m * x_row + xo.off[2 * h + 1]);
+      float2 xf[8];
+      xf[0] = pair_to_f32(u.x, XT()); xf[1] = pair_to_f32(u.y, XT());
+      xf[2] = pair_to_f32(u.z, XT()); xf[3] = pair_to_f32(u.w, XT());
+      xf[4] = pair_to_f32(v.x, XT()); xf[5] = pair_to_f32(v.y, XT());
+      xf[6] = pair_to_f32(v.z, XT()); xf[7] = pair_to_f32(v.w, XT());
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float2 part = __fmul2_rn(wf[r][0], xf[0]);
+#pragma unroll
+        for (int q = 1; q < 8; ++q) part = __ffma2_rn(wf[r][q], xf[q], part);
+        const float s = h ? sc[r].y : sc[r].x;
+        acc[r][m] = __ffma2_rn(make_float2(s, s), part, acc[r][m]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// One tile for one consumer warp holding up to R rows (nr of them real).
+
+template <int FMT, int M, int R, typename XT>
+__device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, const StageLayout<FMT, M>& lay,
+                                             unsigned char* smem, uint32_t full0, uint32_t empty0,
+                                             volatile int* abort_flag, int row0, int nr, int& s,
+                                             uint32_t& parity) {
+  constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const XOffsets<NQ> xo(lane);
+  float2 acc[R][M];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = make_float2(0.f, 0.f);
+  const int wstride = kConsumerWarps * lay.w_row;       // the warp's rows are kConsumerWarps tile rows apart
+  const int scstride = kConsumerWarps * lay.sc_row;
+
+  for (int win = 0; win < wk.nwin; ++win) {
+    if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;
+    if (nr > 0) {
+      const unsigned char* stage = smem + kSmemHeader + (size_t)s * p.stage_bytes;
+      const int blk0 = win * p.steps * 32;
+      const int nsteps = min(p.steps, (p.nblk - blk0 + 31) >> 5);
+      for (int st = 0; st < nsteps; ++st) {
+        const int blk = blk0 + st * 32 + lane;
+        if (blk < p.nblk) {
+          const unsigned char* wrow = stage + warp * lay.w_row + st * kStepBytes + lane * 16;
+          const unsigned char* xs = stage + lay.x_off + st * (64 * E);
+          if constexpr (FMT == FMT_BF16) {
+            body_bf16<M, R, XT>(wrow, wstride, nr, xs + lane * 16, lay.x_row, acc);
+          } else if constexpr (FMT == FMT_FP8) {
+            float none[R];
+            body_fp8<false, M, R, XT>(wrow, wstride, nr, none, xs, lay.x_row, xo, acc);
+          } else if constexpr (FMT == FMT_MXFP8) {
+            float sc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const int rr = min(r, nr - 1);
+              uint32_t e;
+              if (p.scale_mode == SCALES_STAGED)
+                e = stage[lay.sc_off + warp * lay.sc_row + rr * scstride + st * SCB + (lane >> 1)];
+              else
+                e = __ldg(p.scales + (size_t)(row0 + warp + kConsumerWarps * rr) * p.scale_row_bytes + (blk >> 1));
+              sc[r] = e8m0_to_f32(e);
+            }
+            body_fp8<true, M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
+          } else {
+            float2 sc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const int rr = min(r, nr - 1);
+              uint32_t e;
+              if (p.scale_mode == SCALES_STAGED) {
+                e = *reinterpret_cast<const uint16_t*>(stage + lay.sc_off + warp * lay.sc_row + rr * scstride +
+                                                       st * SCB + lane * 2);
+              } else {
+                const int n = row0 + warp + kConsumerWarps * rr;
+                const size_t off = p.scale_mode == SCALES_BLOCKED ? tiled_scale_offset(n, blk * 2, p.ct)
+                                                                   : (size_t)n * p.scale_row_bytes + blk * 2;
+                e = __ldg(reinterpret_cast<const uint16_t*>(p.scales + off));
+              }
+              sc[r] = e4m3x2_to_f32(e);
+            }
+            body_nvfp4<M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8u * s);
+    if (++s == p.stages) { s = 0; parity ^= 1u; }
+  }
+
+  // the two chains, then the lanes: xor-shuffle tree 16, 8, 4, 2, 1; scale once; round once
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (r < nr) {
+      const int n = row0 + warp + kConsumerWarps * r;
+      const float scale = p.row_scale ? __ldg(p.row_scale + n) : 1.0f;
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float v = acc[r][m].x + acc[r][m].y;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, p.row_scale ? v * scale : v);
+      }
+    }
+  }
+  return true;
+}
+
+template <int FMT, int M, typename XT>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ Params p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int RMAX = rows_max(FMT, M);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full0 + 8u * s, 33);                    // 32 cp.async completions + the expect_tx arrival
+      mbar_init(empty0 + 8u * s, kConsumerWarps);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5;
+  if (warp == kConsumerWarps) {
+    producer<FMT, M>(p, smem, full0, empty0, abort_flag);
+  } else {
+    const Walk wk(p);
+    const StageLayout<FMT, M> lay(p);
+    int s = 0;
+    uint32_t parity = 0;
+    bool ok = true;
+    for (int t = 0; t < wk.ntiles && ok; ++t) {
+      const int row0 = wk.lo + t * wk.tile_rows;
+      const int rows = min(wk.tile_rows, wk.hi - row0);
+      const int nr = rows > warp ? (rows - warp + kConsumerWarps - 1) / kConsumerWarps : 0;
+      if (RMAX >= 8 && nr > 4)
+        ok = consume_tile<FMT, M, (RMAX >= 8 ? 8 : RMAX), XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
+                                                                    parity);
+      else if (RMAX >= 4 && nr > 2)
+        ok = consume_tile<FMT, M, (RMAX >= 4 ? 4 : RMAX), XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
+                                                                    parity);
+      else if (RMAX >= 2 && nr > 1)
+        ok = consume_tile<FMT, M, 2, XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
+                                                                    parity);
+      else
+        ok = consume_tile<FMT, M, 1, XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
+                                                                    parity);
+    }
+    if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
+  }
+  // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
+  // memory is handed to the next one (bounded sleep, error path only).
+  if (*abort_flag)
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+}
+
+}  // namespace dg

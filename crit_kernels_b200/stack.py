@@ -1,0 +1,138 @@
+"""Column-sharded NVFP4 projection stack: the multi-GPU form of the decode GEMV.
+
+Each projection's output columns (rows of the [N][K] weight matrix) are split evenly over the ranks of one node: rank r
+holds rows [r*N/P, (r+1)*N/P) of codes, block scales and inverse scales (contiguous slices, no repacking), multiplies
+the full activations by its slice, and an all-gather over NVLink assembles the [M][N] result on every rank. The K
+dimension is never split: a row's sum is computed by one GPU in the order it has on a single GPU, so the gathered
+output is bit-identical to the unsharded one (tests/test_stack_*.py).
+
+The reference has no multi-GPU code; this module is new work on top of the op surface it defines.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from . import get_kernel
+
+
+@dataclass
+class Projection:
+    role: str
+    k: int
+    n: int                      # full output width
+    codes: torch.Tensor         # [n/P][k/2] uint8, this rank's rows
+    scales: torch.Tensor        # [n/P][k/16] E4M3 bytes
+    inverse: torch.Tensor       # [n/P] FP32
+
+
+def random_nvfp4(n, k, device, generator):
+    """A full NVFP4 matrix in the benchmark distribution: uniform E2M1 codes, E4M3 block scales nearest 2^u with
+    u ~ U(-4, 2), global scale 1."""
+    codes = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=device, generator=generator)
+    scales = torch.exp2(torch.rand(n, k // 16, device=device, generator=generator) * 6 - 4).to(torch.float8_e4m3fn)
+    return codes, scales.view(torch.uint8), torch.ones(n, device=device)
+
+
+class StackRun:
+    """One captured pass over the stack at a fixed row count M."""
+
+    def __init__(self, stack, m):
+        self.stack, self.m = stack, m
+        dev = stack.device
+        g = torch.Generator().manual_seed(4242 + m)
+        self.x_host = {role: torch.randn(m, k, generator=g).to(torch.bfloat16).pin_memory()
+                       for role, k, _ in stack.roles}
+        self.x = {role: t.to(dev) for role, t in self.x_host.items()}
+        self.shard = {role: torch.empty(m, n // stack.world, dtype=torch.bfloat16, device=dev)
+                      for role, _, n in stack.roles}
+        self.full = {role: torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16, device=dev)
+                     for role, _, n in stack.roles}
+        last = stack.roles[-1][0]
+        self.out_host = torch.empty_like(self.full[last], device="cpu").pin_memory()
+        self.h2d_bytes = sum(t.numel() * 2 for t in self.x_host.values())
+        self.d2h_bytes = self.out_host.numel() * 2
+        self.kernel_launches = len(stack.projections)
+        self.graph = None
+
+    def eager(self, keep=None):
+        """Runs the pass on the current stream; `keep` collects every projection's gathered [M][N] output."""
+        st = self.stack
+        for p in st.projections:
+            st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
+            if st.world > 1:
+                dist.all_gather_into_tensor(self.full[p.role].view(-1, self.shard[p.role].shape[1]),
+                                            self.shard[p.role], group=st.group)
+                if keep is not None:
+                    keep.append(self.full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone())
+            elif keep is not None:
+                keep.append(self.shard[p.role].clone())
+
+    def capture(self):
+        side = torch.cuda.Stream(device=self.stack.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.eager()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.eager()
+        return self
+
+    def replay(self):
+        self.graph.replay()
+
+    def replay_e2e(self):
+        for role, host in self.x_host.items():
+            self.x[role].copy_(host, non_blocking=True)
+        self.graph.replay()
+        last = self.stack.roles[-1][0]
+        src = self.full[last] if self.stack.world > 1 else self.shard[last].view_as(self.out_host)
+        self.out_host.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+
+
+@dataclass
+class ShardedStack:
+    projections: list
+    roles: tuple
+    rank: int
+    world: int
+    device: torch.device
+    group: object = None
+    kernel: object = field(default_factory=get_kernel)
+
+    @property
+    def gather_kind(self):
+        return "none (1 GPU)" if self.world == 1 else "NCCL all_gather_into_tensor after every GEMV, inside the graph"
+
+    @classmethod
+    def random(cls, layers, roles, rank, world, device, seed=0, group=None):
+        """`layers` x `roles` projections; every rank draws the same full matrix from the same seed and keeps its
+        rows, so the shards of all ranks together are exactly the matrix a single GPU would hold."""
+        projections = []
+        for layer in range(layers):
+            for idx, (role, k, n) in enumerate(roles):
+                if n % world:
+                    raise ValueError(f"{role}: N={n} does not split over {world} ranks")
+                g = torch.Generator(device=device).manual_seed(seed * 1000003 + layer * 16 + idx)
+                codes, scales, inverse = random_nvfp4(n, k, device, g)
+                lo, hi = rank * n // world, (rank + 1) * n // world
+                projections.append(Projection(role, k, n, codes[lo:hi].clone(), scales[lo:hi].clone(),
+                                              inverse[lo:hi].clone()))
+                del codes, scales, inverse
+        return cls(projections, tuple(roles), rank, world, device, group)
+
+    def capture(self, m):
+        return StackRun(self, m).capture()
+
+    def run(self, m):
+        """Eager pass; returns every projection's gathered output (for tests)."""
+        keep = []
+        StackRun(self, m).eager(keep)
+        torch.cuda.synchronize()
+        return keep

@@ -1,0 +1,157 @@
+// Torch op registration and argument checks over the C ABI (include/decode_gemv_b200.h).
+//
+// The schemas are those of the reference (decode-gemv/torch-ext/torch_binding.cpp:7-10), CUDA implementations only,
+// and every refusal of its entry points (decode-gemv/decode_gemv_cuda/binding.cu:19-118) is kept: a violated rule
+// raises c10::Error, a Python RuntimeError. Nothing here allocates or waits for the device, and the launch goes to
+// the current stream of x's device, so a CUDA graph captures the calls.
+#include "torch_binding.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime_api.h>
+#include <torch/library.h>
+
+#include <cstdint>
+
+#include "../../include/decode_gemv_b200.h"
+
+#ifndef DG_TORCH_NAMESPACE
+#define DG_TORCH_NAMESPACE _decode_gemv_b200
+#endif
+
+namespace {
+
+bool on_boundary(const torch::Tensor& t, std::uintptr_t bytes) {
+  return reinterpret_cast<std::uintptr_t>(t.data_ptr()) % bytes == 0;
+}
+
+// x: 2-D CUDA, 1..16 rows, unit inner stride, rows 16 bytes apart on a 16-byte base; BF16, or FP16 where allowed.
+void require_activations(const torch::Tensor& x, bool fp16_ok, const char* op) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2, op, ": x must be a 2-D CUDA tensor [rows][K]");
+  TORCH_CHECK(x.size(0) >= 1 && x.size(0) <= DG_MAX_ROWS, op, ": x has ", x.size(0), " rows; 1 to ", DG_MAX_ROWS,
+              " are supported");
+  TORCH_CHECK(x.stride(1) == 1 && x.stride(0) % 8 == 0 && on_boundary(x, 16), op,
+              ": rows of x must be contiguous and start on 16-byte boundaries");
+  if (fp16_ok) {
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kFloat16, op,
+                ": x must be BF16 or FP16");
+  } else {
+    TORCH_CHECK(x.scalar_type() == torch::kBFloat16, op, ": x must be BF16");
+  }
+}
+
+void require_output(const torch::Tensor& out, const torch::Tensor& x, int64_t n, const char* op) {
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.size(0) == x.size(0) && out.size(1) == n && out.stride(1) == 1,
+              op, ": out must be [rows][N] with contiguous rows");
+  TORCH_CHECK(out.scalar_type() == torch::kFloat32 || out.scalar_type() == x.scalar_type(), op,
+              ": out must be FP32 or have x's dtype");
+}
+
+void require_same_device(const torch::Tensor& x, std::initializer_list<const torch::Tensor*> rest, const char* op) {
+  for (const torch::Tensor* t : rest)
+    TORCH_CHECK(t->device() == x.device(), op, ": all tensors must be on x's device (", x.device(), "), found ",
+                t->device());
+}
+
+void require_success(int code, const char* op) {
+  TORCH_CHECK(code == 0, op, ": ", cudaGetErrorString(static_cast<cudaError_t>(code)));
+}
+
+}  // namespace
+
+void gemv(const torch::Tensor& x, const torch::Tensor& codes, const torch::Tensor& scales,
+          const torch::Tensor& inverse, bool blocked, torch::Tensor& out) {
+  const char* op = "gemv";
+  require_activations(x, true, op);
+  const int64_t n = codes.size(0), k = x.size(1);
+  TORCH_CHECK(k % 32 == 0, op, ": K must be a multiple of 32, got ", k);
+  TORCH_CHECK(codes.is_cuda() && codes.dim() == 2 && codes.is_contiguous() && codes.scalar_type() == torch::kUInt8 &&
+                  codes.size(1) * 2 == k && on_boundary(codes, 16),
+              op, ": codes must be contiguous uint8 [N][K / 2] on a 16-byte boundary");
+  TORCH_CHECK(scales.is_cuda() && scales.is_contiguous() && scales.element_size() == 1 && on_boundary(scales, 2), op,
+              ": scales must be contiguous E4M3 bytes on a 2-byte boundary");
+  if (blocked) {
+    TORCH_CHECK(scales.numel() == ((n + 127) / 128) * 128 * ((k / 16 + 3) / 4) * 4, op,
+                ": blocked scales must hold the 128 x 4 tiles of [N][K / 16] (rows padded to 128, blocks to 4)");
+  } else {
+    TORCH_CHECK(scales.dim() == 2 && scales.size(0) == n && scales.size(1) * 16 == k, op,
+                ": scales must be E4M3 bytes [N][K / 16]");
+  }
+  TORCH_CHECK(inverse.is_cuda() && inverse.is_contiguous() && inverse.scalar_type() == torch::kFloat32 &&
+                  inverse.numel() == n && on_boundary(inverse, 4),
+              op, ": inverse must be contiguous FP32 [N]");
+  require_output(out, x, n, op);
+  require_same_device(x, {&codes, &scales, &inverse, &out}, op);
+  const c10::cuda::CUDAGuard guard(x.device());
+  require_success(dg_enqueue_nvfp4(x.data_ptr(), static_cast<int>(x.stride(0)), x.scalar_type() == torch::kBFloat16,
+                                   codes.data_ptr<std::uint8_t>(), static_cast<const std::uint8_t*>(scales.data_ptr()),
+                                   blocked, inverse.data_ptr<float>(), out.data_ptr(), static_cast<int>(out.stride(0)),
+                                   out.scalar_type() == torch::kFloat32 ? 0 : 1, static_cast<int>(x.size(0)),
+                                   static_cast<int>(n), static_cast<int>(k), at::cuda::getCurrentCUDAStream().stream()),
+                  op);
+}
+
+void gemv_fp8(const torch::Tensor& x, const torch::Tensor& codes, const torch::Tensor& scales, torch::Tensor& out) {
+  const char* op = "gemv_fp8";
+  require_activations(x, true, op);
+  const int64_t n = codes.size(0), k = x.size(1);
+  TORCH_CHECK(codes.is_cuda() && codes.dim() == 2 && codes.is_contiguous() && codes.element_size() == 1 &&
+                  codes.size(1) == k && k % 16 == 0 && on_boundary(codes, 16),
+              op, ": codes must be contiguous E4M3 bytes [N][K] on a 16-byte boundary, K a multiple of 16");
+  TORCH_CHECK(scales.is_cuda() && scales.is_contiguous(), op, ": scales must be a contiguous CUDA tensor");
+  const bool mx = scales.scalar_type() == torch::kUInt8;
+  if (mx) {
+    TORCH_CHECK(scales.dim() == 2 && scales.size(0) == n && k % 32 == 0 && scales.size(1) * 32 == k, op,
+                ": MXFP8 scales must be E8M0 bytes [N][K / 32], K a multiple of 32");
+  } else {
+    TORCH_CHECK(scales.scalar_type() == torch::kFloat32 && scales.numel() == n && on_boundary(scales, 4), op,
+                ": row scales must be FP32 [N] (or uint8 E8M0 [N][K / 32] for MXFP8)");
+  }
+  require_output(out, x, n, op);
+  require_same_device(x, {&codes, &scales, &out}, op);
+  const c10::cuda::CUDAGuard guard(x.device());
+  require_success(dg_enqueue_fp8(x.data_ptr(), static_cast<int>(x.stride(0)), x.scalar_type() == torch::kBFloat16,
+                                 static_cast<const std::uint8_t*>(codes.data_ptr()),
+                                 mx ? nullptr : scales.data_ptr<float>(),
+                                 mx ? scales.data_ptr<std::uint8_t>() : nullptr, out.data_ptr(),
+                                 static_cast<int>(out.stride(0)), out.scalar_type() == torch::kFloat32 ? 0 : 1,
+                                 static_cast<int>(x.size(0)), static_cast<int>(n), static_cast<int>(k),
+                                 at::cuda::getCurrentCUDAStream().stream()),
+                  op);
+}
+
+void gemv_bf16(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& out) {
+  const char* op = "gemv_bf16";
+  require_activations(x, false, op);
+  const int64_t n = w.size(0), k = x.size(1);
+  TORCH_CHECK(w.is_cuda() && w.dim() == 2 && w.is_contiguous() && w.scalar_type() == torch::kBFloat16 &&
+                  w.size(1) == k && k % 8 == 0 && on_boundary(w, 16),
+              op, ": w must be contiguous BF16 [N][K] on a 16-byte boundary, K a multiple of 8");
+  require_output(out, x, n, op);
+  require_same_device(x, {&w, &out}, op);
+  const c10::cuda::CUDAGuard guard(x.device());
+  require_success(dg_enqueue_bf16(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), out.data_ptr(),
+                                  static_cast<int>(out.stride(0)), out.scalar_type() == torch::kFloat32 ? 0 : 1,
+                                  static_cast<int>(x.size(0)), static_cast<int>(n), static_cast<int>(k),
+                                  at::cuda::getCurrentCUDAStream().stream()),
+                  op);
+}
+
+int64_t hardware_decode(const torch::Tensor& device_of) {
+  const c10::cuda::CUDAGuard guard(device_of.device());
+  return dg_hardware_decode();
+}
+
+TORCH_LIBRARY(DG_TORCH_NAMESPACE, ops) {
+  ops.def("gemv(Tensor x, Tensor codes, Tensor scales, Tensor inverse, bool blocked, Tensor! out) -> ()");
+  ops.def("gemv_fp8(Tensor x, Tensor codes, Tensor scales, Tensor! out) -> ()");
+  ops.def("gemv_bf16(Tensor x, Tensor w, Tensor! out) -> ()");
+  ops.def("hardware_decode(Tensor device_of) -> int");
+}
+
+TORCH_LIBRARY_IMPL(DG_TORCH_NAMESPACE, CUDA, ops) {
+  ops.impl("gemv", &gemv);
+  ops.impl("gemv_fp8", &gemv_fp8);
+  ops.impl("gemv_bf16", &gemv_bf16);
+  ops.impl("hardware_decode", &hardware_decode);
+}

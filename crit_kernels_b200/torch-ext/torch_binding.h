@@ -1,0 +1,16 @@
+// Torch entry points of the B200 decode GEMVs: the op surface of the reference package decode-gemv
+// (decode-gemv/torch-ext/torch_binding.h:8-16), same argument order and meaning.
+#pragma once
+
+#include <torch/types.h>
+
+// x [M][K] (M 1..16) BF16 or FP16; codes [N][K / 2] uint8; scales E4M3 bytes, row major [N][K / 16] or, blocked,
+// cuBLASLt's 128 x 4 tiles; inverse [N] FP32; out [M][N] FP32 or x's dtype.
+void gemv(const torch::Tensor& x, const torch::Tensor& codes, const torch::Tensor& scales,
+          const torch::Tensor& inverse, bool blocked, torch::Tensor& out);
+// x as above; codes [N][K] E4M3 bytes; scales FP32 [N] (row scales) or uint8 [N][K / 32] (MXFP8 exponents).
+void gemv_fp8(const torch::Tensor& x, const torch::Tensor& codes, const torch::Tensor& scales, torch::Tensor& out);
+// x [M][K] BF16; w [N][K] BF16; out FP32 or BF16.
+void gemv_bf16(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& out);
+// 1: E2M1 decodes by the hardware conversion on device_of's device (always, for this sm_100a build).
+int64_t hardware_decode(const torch::Tensor& device_of);

@@ -1,0 +1,72 @@
+/* C ABI of the B200 decode-GEMV library (libdecode_gemv_b200.so).
+ *
+ * These entry points are what a binding for the reference package decode-gemv would call in place of its raw CUDA API
+ * (decode-gemv/decode_gemv_cuda/decode_gemv.h:30-43): plain pointers and sizes, device pointers unless said otherwise,
+ * a cudaStream_t passed as void*. Every function returns a cudaError_t value as int (0 = cudaSuccess;
+ * 1 = cudaErrorInvalidValue for a shape, alignment or row-count the kernels cannot read). Nothing allocates, nothing
+ * waits for the device: the enqueue calls can be captured in a CUDA graph, as the reference's can (binding.cu:1-2).
+ *
+ * Common rules (the reference's, binding.cu:19-63 and decode_gemv.cu:382, 396, 405):
+ *   x      [M][K] BF16 (x_is_bf16 = 1) or FP16 (0), rows ldx elements apart, ldx % 8 == 0, base on 16 bytes, M 1..16
+ *   out    [M][N], rows ldo elements apart; out_kind 0 = FP32, 1 = x's 16-bit type
+ *   a row's result is the same bits whatever M is and whatever other rows the matrix holds (summation order is a
+ *   function of K and the format only), so an N-slice of a matrix gives the bits of the whole matrix's rows.
+ */
+#ifndef DECODE_GEMV_B200_H_
+#define DECODE_GEMV_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DG_MAX_ROWS 16
+
+#if defined(__GNUC__)
+#define DG_API __attribute__((visibility("default")))
+#else
+#define DG_API
+#endif
+
+/* NVFP4 W4A16. Replaces enqueue_gemv (decode_gemv.h:30-32, decode_gemv.cu:378-392).
+ * out[m][n] = inverse[n] * sum_k x[m][k] * e2m1(codes[n][k]) * e4m3(scales[n][k / 16])
+ * codes [N][K/2] bytes on 16 bytes (element 2i in the low nibble of byte i), K % 32 == 0, K >= 32;
+ * scales E4M3 bytes on 2 bytes: row major [N][K/16], or (blocked = 1) cuBLASLt's 128 x 4 tiles with rows padded to
+ * 128 and blocks to 4; inverse [N] FP32. */
+DG_API int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales, int blocked,
+                     const float* inverse, void* out, int ldo, int out_kind, int M, int N, int K, void* stream);
+
+/* FP8 E4M3 W8A16. Replaces enqueue_gemv_fp8 (decode_gemv.h:34-36, decode_gemv.cu:402-417).
+ * Exactly one of row_scale ([N] FP32: out = row_scale[n] * sum) and mx_scale ([N][K/32] E8M0 bytes, MXFP8:
+ * each weight times 2^(e - 127)) is non-null. codes [N][K] bytes on 16 bytes, K % 16 == 0 (32 for MXFP8), K >= 16. */
+DG_API int dg_enqueue_fp8(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const float* row_scale,
+                   const uint8_t* mx_scale, void* out, int ldo, int out_kind, int M, int N, int K, void* stream);
+
+/* BF16 weights. Replaces enqueue_gemv_bf16 (decode_gemv.h:38-39, decode_gemv.cu:394-400).
+ * w [N][K] BF16 on 16 bytes, K % 8 == 0, K >= 8; x BF16; out_kind 0 = FP32, 1 = BF16. */
+DG_API int dg_enqueue_bf16(const void* x, int ldx, const void* w, void* out, int ldo, int out_kind, int M, int N, int K,
+                    void* stream);
+
+/* 1 when the current device runs this build's hardware E2M1 conversion (cvt.rn.f16x2.e2m1x2; always, on the sm_100a
+ * target this library is built for), -1 when the current device cannot run the library. Replaces hardware_decode
+ * (decode_gemv.h:43, decode_gemv.cu:419-427); unlike it, allocates nothing and launches nothing. */
+DG_API int dg_hardware_decode(void);
+
+/* The launch a call with these sizes makes, for benches and tests: fmt 0 BF16, 1 FP8, 2 MXFP8, 3 NVFP4.
+ * plan[0] = CTAs, [1] = rows per consumer warp and tile, [2] = 512-byte steps per ring stage, [3] = ring stages,
+ * [4] = bytes per stage, [5] = dynamic shared memory bytes. Host only; returns 0, or 1 for sizes the kernels refuse. */
+DG_API int dg_plan(int fmt, int M, int N, int K, int plan[6]);
+
+/* Reads and clears the current device's error word: bit 0 a producer wait ran out, bit 1 a consumer wait ran out
+ * (a bounded wait inside a kernel gave up; the call's output is then incomplete). Synchronises the device. Host
+ * diagnostic, not part of the hot path; returns the word (0 = clean) or a negative cudaError_t. */
+DG_API int dg_take_status(void);
+
+/* Library version: 100 * major + minor. */
+DG_API int dg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DECODE_GEMV_B200_H_ */

@@ -1,0 +1,53 @@
+"""TEST INFRASTRUCTURE ONLY. Builds oracle/_ref/libdecode_gemv_ref.so: the reference's own CUDA source
+(decode-gemv/decode_gemv_cuda/decode_gemv.cu, two files, no build system) compiled for sm_100a from where it lies in
+the reference checkout, plus oracle/ref_shim.cu. No reference source is copied; only the binary lands in oracle/_ref/
+(git-ignored, shipped to the GPU box). Without the checkout this is a no-op and whatever was built earlier is used.
+
+    python -m oracle.build_ref [path/to/reference]
+"""
+import ctypes
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT_DIR = os.path.join(HERE, "_ref")
+LIB = os.path.join(OUT_DIR, "libdecode_gemv_ref.so")
+NVCC = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
+
+
+def build(reference="/root/reference", verbose=True):
+    src_dir = os.path.join(reference, "decode-gemv", "decode_gemv_cuda")
+    src = os.path.join(src_dir, "decode_gemv.cu")
+    shim = os.path.join(HERE, "ref_shim.cu")
+    if not os.path.exists(src):
+        return os.path.exists(LIB)
+    if os.path.exists(LIB) and os.path.getmtime(LIB) > max(os.path.getmtime(src), os.path.getmtime(shim)):
+        return True
+    os.makedirs(OUT_DIR, exist_ok=True)
+    # -gencode ...100a: the reference switches to the hardware E2M1 conversion on this target (decode_gemv.cu:10-14)
+    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
+           "-Xcompiler", "-fvisibility=hidden", "-cudart", "static", f"-I{src_dir}", src, shim, "-o", LIB]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+    return True
+
+
+def load():
+    """The reference library, or None when it was never built."""
+    if not os.path.exists(LIB):
+        return None
+    lib = ctypes.CDLL(LIB)
+    p, i = ctypes.c_void_p, ctypes.c_int
+    lib.ref_enqueue_nvfp4.argtypes = [p, i, i, p, p, i, p, p, i, i, i, i, i, p]
+    lib.ref_enqueue_fp8.argtypes = [p, i, i, p, p, p, p, i, i, i, i, i, p]
+    lib.ref_enqueue_bf16.argtypes = [p, i, p, p, i, i, i, i, i, p]
+    for f in (lib.ref_enqueue_nvfp4, lib.ref_enqueue_fp8, lib.ref_enqueue_bf16, lib.ref_hardware_decode):
+        f.restype = i
+    return lib
+
+
+if __name__ == "__main__":
+    ok = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    print("built" if ok else "reference checkout not found; nothing built")

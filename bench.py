@@ -267,6 +267,28 @@ def run_stack(args, dev, rank, world, ms=STACK_MS, layers=None):
             "launches": args.steps * sum(runs[m].kernel_launches for m in ms), "gather": model.gather_kind}
 
 
+def run_case(args):
+    """`--case fmt:M:N:K`: seeded inputs in the benchmark distributions, --warmup + --steps calls, device time."""
+    import crit_kernels_b200
+    from oracle import workloads as wl
+    fmt, m, n, kk = args.case.split(":")
+    m, n, kk = int(m), int(n), int(kk)
+    dev = torch.device("cuda", 0)
+    k = crit_kernels_b200.get_kernel("crit-labs/decode-gemv", version=1)
+    host = {"nvfp4": lambda: wl.cfg_nvfp4(n, kk), "fp8": lambda: wl.cfg_fp8(n, kk), "mxfp8": lambda: wl.cfg_mxfp8(n, kk),
+            "bf16": lambda: (wl.cfg_bf16(n, kk),)}[fmt]()
+    t = tuple(a.to(dev) for a in host)
+    x = wl.activations(m, kk).to(dev)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    call = {"nvfp4": lambda: k.gemv(x, t[0], t[1], t[2], out), "fp8": lambda: k.gemv_fp8(x, t[0], t[1], out),
+            "mxfp8": lambda: k.gemv_fp8(x, t[0], t[1], out), "bf16": lambda: k.gemv_bf16(x, t[0], out)}[fmt]
+    for _ in range(args.warmup):
+        call()
+    ms = time_region(call, args.steps) / args.steps
+    nbytes = wl.weight_bytes(fmt, n, kk)
+    print(json.dumps({"case": args.case, "us": ms * 1e3, "GBps": nbytes / ms / 1e6, "weight_bytes": nbytes}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -275,10 +297,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "c1", "stack"])
     ap.add_argument("--layers", type=int, default=None, help="stack depth (default 80)")
+    ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
+                    help="run `--steps` calls of one GEMV (fmt in bf16, fp8, mxfp8, nvfp4) and exit: the small case "
+                         "profilers capture")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.case:
+        run_case(args)
         return
     rank, world, local = dist_env()
     if not torch.cuda.is_available():

@@ -25,5 +25,5 @@ def get_kernel(repo_id: str = REPO_ID, version: int | None = None, **_):
 
 def build(verbose: bool = False):
     """Compiles the CUDA library and the torch op library in-tree (needs nvcc and g++, no GPU)."""
-    from . import build as _build
-    return _build.build(verbose=verbose)
+    from . import builder
+    return builder.build(verbose=verbose)

@@ -5,7 +5,7 @@
   decode_gemv/_decode_gemv_b200.so    the torch op library over that ABI (torch-ext/torch_binding.cpp); g++
 
 Objects land in build/obj and are rebuilt only when a source or header is newer. Run `python -m
-crit_kernels_b200.build` (or call build()); nvcc cross-compiles, so no GPU is needed.
+crit_kernels_b200.builder` (or call build()); nvcc cross-compiles, so no GPU is needed.
 """
 from __future__ import annotations
 

@@ -31,7 +31,7 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         if not os.path.exists(_PATH):
-            raise OSError(f"{_PATH} is missing: build it with `python -m crit_kernels_b200.build`")
+            raise OSError(f"{_PATH} is missing: build it with `python -m crit_kernels_b200.builder`")
         lib = ctypes.CDLL(_PATH)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)

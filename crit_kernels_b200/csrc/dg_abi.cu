@@ -7,6 +7,8 @@
 
 #include <atomic>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 
 #include "../../include/decode_gemv_b200.h"
 #include "dg_kernel.cuh"
@@ -69,26 +71,36 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // Launch shape: a speed choice from (format, M, N, K, SM count) only; no row's bits depend on it.
 //   CTAs            one per SM, fewer when the matrix has under one row per consumer warp and SM
 //   rows per warp   the most the kernel holds (rows_max), less when a CTA's range is short
-//   steps           512-byte steps per ring stage: about 24 KB of weights per stage, activations under 32 KB
+//   steps           512-byte steps per ring stage: at least two (bulk copies of 1 KB or more keep the copy issue
+//                   rate off the critical path), more when a tile has few rows (about 24 KB of weights per stage),
+//                   activations under 32 KB per stage
 //   stages          as many as fit in shared memory, at most kMaxStages
 bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem) {
   const FormatInfo f = kFormats[fmt];
+  const int cw = dg::consumer_warps(fmt, M);
   const long long row_bits = (long long)K * 128 / f.e;   // 16 bytes per e elements
   p.row_bytes = (int)(row_bits / 8);
   p.nblk = p.row_bytes / 16;
-  ctas = sms < ceil_div(N, dg::kConsumerWarps) ? sms : ceil_div(N, dg::kConsumerWarps);
+  ctas = sms < ceil_div(N, cw) ? sms : ceil_div(N, cw);
   const int rows_per_cta = ceil_div(N, ctas);
-  const int per_warp = ceil_div(rows_per_cta, dg::kConsumerWarps);
-  const int rmax = dg::rows_max(fmt, M);
+  const int per_warp = ceil_div(rows_per_cta, cw);
+  int rmax = dg::rows_max(fmt, M);
+  // Tuning aid: DG_FORCE_PLAN="rows,steps" caps the rows per warp and fixes the steps per stage (read once).
+  static const char* forced = std::getenv("DG_FORCE_PLAN");
+  int force_rows = 0, force_steps = 0;
+  if (forced && std::sscanf(forced, "%d,%d", &force_rows, &force_steps) >= 1 && force_rows >= 1 && force_rows < rmax)
+    rmax = force_rows;
   p.rows_per_warp = per_warp < rmax ? per_warp : rmax;
-  const int rows_cap = dg::kConsumerWarps * p.rows_per_warp;
+  const int rows_cap = cw * p.rows_per_warp;
   const int w_step = rows_cap * (dg::kStepBytes + f.scb);
   const int x_step = M * 64 * f.e;
   const int row_steps = ceil_div(p.nblk, 32);
   int steps = ceil_div(24576, w_step);
-  if (steps > row_steps) steps = row_steps;
+  if (steps < 2) steps = 2;
   if (steps > 8) steps = 8;
+  if (steps > row_steps) steps = row_steps;
   while (steps > 1 && steps * x_step > 32768) --steps;
+  if (force_steps >= 1) steps = force_steps < row_steps ? force_steps : row_steps;
   if (steps < 1) steps = 1;
   p.steps = steps;
   p.stage_bytes = (steps * (w_step + x_step) + 127) & ~127;
@@ -109,7 +121,8 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
   p.status = st->status;
   void* args[] = {&p};
-  const cudaError_t e = cudaLaunchKernel(kTables[table][M - 1], dim3(ctas), dim3(dg::kThreads), args, smem, stream);
+  const int threads = 32 * (dg::consumer_warps(fmt, M) + dg::producer_warps(fmt, M));
+  const cudaError_t e = cudaLaunchKernel(kTables[table][M - 1], dim3(ctas), dim3(threads), args, smem, stream);
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 

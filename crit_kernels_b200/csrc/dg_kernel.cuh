@@ -5,13 +5,14 @@
 // :191 bf16_kernel, :285 fp8_kernel). Same formats, same contract (FP32 sums whose order never depends on the row
 // count), a different machine mapping:
 //
-//   * one persistent CTA per SM: 7 consumer warps + 1 producer warp. The matrix rows are split into one contiguous
-//     range per CTA; a range is walked in tiles of 7*r rows (r rows per consumer warp) and each tile in K windows.
-//   * the producer warp streams every window of a tile into a shared-memory ring: one cp.async.bulk (TMA 1-D bulk
-//     copy, mbarrier complete_tx) per weight row (and per row of block scales), issued by 32 lanes in parallel, plus
-//     the matching window of the activations as 16-byte cp.async copies into a bank-swizzled layout. Bytes in flight
-//     are set by the ring (up to ~200 KB per SM), not by registers.
-//   * consumer warp w owns rows w, w+7, ... of the tile. Lane l owns the 16-byte blocks l, l+32, ... of each row and
+//   * one persistent CTA per SM: C consumer warps + P producer warps (12 + 4 or 6 + 2, by format and M). The matrix
+//     rows are split into one contiguous range per CTA; a range is walked in tiles of C*r rows (r rows per consumer
+//     warp) and each tile in K windows.
+//   * the producer warps stream every window of a tile into a shared-memory ring: one cp.async.bulk (TMA 1-D bulk
+//     copy, mbarrier complete_tx) per weight row (and per row of block scales), issued by the producers' lanes in
+//     parallel, plus the matching window of the activations as 16-byte cp.async copies into a bank-swizzled layout.
+//     Bytes in flight are set by the ring (up to ~200 KB per SM), not by registers.
+//   * consumer warp w owns rows w, w+C, ... of the tile. Lane l owns the 16-byte blocks l, l+32, ... of each row and
 //     keeps two FP32 chains per (row, m): even and odd elements, advanced together by one packed fma.rn.f32x2. The
 //     chains visit the blocks in ascending order, the two chains are added, and one xor-shuffle tree (16, 8, 4, 2, 1)
 //     adds the lanes; the row scale multiplies once and the result is rounded once to the output type.
@@ -35,8 +36,6 @@ enum : int { FMT_BF16 = 0, FMT_FP8 = 1, FMT_MXFP8 = 2, FMT_NVFP4 = 3 };
 enum : int { SCALES_NONE = 0, SCALES_STAGED = 1, SCALES_DIRECT = 2, SCALES_BLOCKED = 3 };
 enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2 };
 
-constexpr int kConsumerWarps = 7;   // + 1 producer = 8 warps: two per SM sub-partition, 255 registers each
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxStages = 12;
 constexpr int kStepBytes = 512;            // 32 lanes x 16 bytes of one weight row
 constexpr int kSmemHeader = 256;           // mbarriers + abort flag
@@ -53,10 +52,16 @@ template <> struct Format<FMT_FP8>   { static constexpr int E = 16, SCB = 0;  };
 template <> struct Format<FMT_MXFP8> { static constexpr int E = 16, SCB = 16; };   // step of one row
 template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 
-// Rows a consumer warp may hold at once (a register-budget choice; never changes a row's bits).
-__host__ __device__ constexpr int rows_max(int fmt, int m) {
-  return fmt == FMT_NVFP4 ? (m <= 8 ? 4 : 2) : (m <= 4 ? 8 : 4);
-}
+// CTA shape per (format, M): a speed choice, never a row's bits.
+//   few activation rows   the kernel is HBM-bound: 12 consumer + 4 producer warps (128 registers each). One warp
+//                         issues a bulk copy every ~60 clocks, so four producers keep 1 KB copies above the HBM rate.
+//   more activation rows  the kernel is FP32-FMA-bound: 6 consumer + 2 producer warps, 255 registers each for the
+//                         accumulators of 3-4 rows x M.
+__host__ __device__ constexpr bool few_rows(int fmt, int m) { return fmt == FMT_NVFP4 ? m <= 2 : m <= 4; }
+__host__ __device__ constexpr int consumer_warps(int fmt, int m) { return few_rows(fmt, m) ? 12 : 6; }
+__host__ __device__ constexpr int producer_warps(int fmt, int m) { return few_rows(fmt, m) ? 4 : 2; }
+// Rows a consumer warp holds at once (register budget).
+__host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }
 
 struct Params {
   const void* x;             // [M][ldx] BF16 or FP16
@@ -74,7 +79,7 @@ struct Params {
   int ct;                    // tiled scales: 4-block tiles per tile row
   int steps;                 // 512-byte steps per ring stage
   int stages;                // ring depth
-  int rows_per_warp;         // r: a full tile is kConsumerWarps * r rows
+  int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
 };
 
@@ -109,7 +114,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const unsigned long long start = global_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -173,14 +178,15 @@ __device__ __forceinline__ void store_out(void* out, int kind, size_t idx, float
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Tile walk shared by producer and consumers: CTA c owns rows [lo, hi); tiles of kConsumerWarps * r rows, the last one shorter.
+// Tile walk shared by producers and consumers: CTA c owns rows [lo, hi); tiles of CW * r rows, the last one shorter.
 
+template <int CW>
 struct Walk {
   int lo, hi, tile_rows, ntiles, nwin, win_bytes;
   __device__ __forceinline__ Walk(const Params& p) {
     lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
     hi = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
-    tile_rows = kConsumerWarps * p.rows_per_warp;
+    tile_rows = CW * p.rows_per_warp;
     ntiles = (hi - lo + tile_rows - 1) / tile_rows;
     win_bytes = p.steps * kStepBytes;
     nwin = (p.row_bytes + win_bytes - 1) / win_bytes;
@@ -188,12 +194,12 @@ struct Walk {
 };
 
 // Shared-memory stage: [weights rows_cap x win_bytes][scales rows_cap x steps*SCB][x M x steps*64*E bytes].
-template <int FMT, int M>
+template <int FMT, int M, int CW>
 struct StageLayout {
   static constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB;
   int w_row, sc_row, x_row, sc_off, x_off;
   __device__ __forceinline__ StageLayout(const Params& p) {
-    const int rows_cap = kConsumerWarps * p.rows_per_warp;
+    const int rows_cap = CW * p.rows_per_warp;
     w_row = p.steps * kStepBytes;
     sc_row = p.steps * SCB;
     x_row = p.steps * 64 * E;
@@ -208,15 +214,14 @@ template <int NQ>
 __device__ __forceinline__ int swizzle_slot(int s) { return s ^ ((s >> 3) & (NQ - 1)); }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Producer warp.
+// Producer warps: `pl` is this thread's index among the 32 * PW producer lanes.
 
-template <int FMT, int M>
+template <int FMT, int M, int CW, int PW>
 __device__ __forceinline__ void producer(const Params& p, unsigned char* smem, uint32_t full0, uint32_t empty0,
-                                         volatile int* abort_flag) {
-  constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
-  const int lane = threadIdx.x & 31;
-  const Walk wk(p);
-  const StageLayout<FMT, M> lay(p);
+                                         volatile int* abort_flag, int pl) {
+  constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8, PL = 32 * PW;
+  const Walk<CW> wk(p);
+  const StageLayout<FMT, M, CW> lay(p);
   const uint32_t ring = smem_addr(smem) + kSmemHeader;
   const bool staged = SCB != 0 && p.scale_mode == SCALES_STAGED;
   const unsigned char* xg = reinterpret_cast<const unsigned char*>(p.x);
@@ -228,31 +233,32 @@ __device__ __forceinline__ void producer(const Params& p, unsigned char* smem, u
     for (int win = 0; win < wk.nwin; ++win) {
       const uint32_t full = full0 + 8u * s, empty = empty0 + 8u * s;
       if (!mbar_wait(empty, parity ^ 1u, abort_flag)) {
-        if (lane == 0 && p.status) atomicOr(p.status, kStatusProducerTimeout);
+        if ((pl & 31) == 0 && p.status) atomicOr(p.status, kStatusProducerTimeout);
         return;
       }
       const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
       const int byte0 = win * wk.win_bytes;
       const int wbytes = min(wk.win_bytes, p.row_bytes - byte0);
-      // activations of this window: wbytes / 16 blocks of E elements per row, 16 bytes (8 elements) per copy
-      const int slots = (wbytes >> 4) * NQ;
-      const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
-      for (int c = lane; c < M * slots; c += 32) {
-        const int m = c / slots, sl = c - m * slots;
-        cp_async16(stage + lay.x_off + m * lay.x_row + swizzle_slot<NQ>(sl) * 16,
-                   xg + (size_t)m * p.ldx * 2 + xbyte0 + (size_t)sl * 16);
-      }
-      cp_async_arrive_noinc(full);
-      const int scbytes = staged ? (wbytes >> 9) * SCB + (((wbytes & 511) * SCB) >> 9) : 0;
-      if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)rows * (uint32_t)(wbytes + scbytes));
-      __syncwarp();
-      for (int r = lane; r < rows; r += 32) {
+      const int scbytes = staged ? (wbytes * SCB) >> 9 : 0;
+      // One arrival carries the byte count of every bulk copy of the stage; completions may land before it (the
+      // phase cannot end while this arrival and the producers' cp.async arrivals are outstanding).
+      if (pl == 0) mbar_arrive_expect_tx(full, (uint32_t)rows * (uint32_t)(wbytes + scbytes));
+      for (int r = pl; r < rows; r += PL) {
         const size_t n = (size_t)(row0 + r);
         bulk_g2s(stage + r * lay.w_row, p.w + n * p.row_bytes + byte0, (uint32_t)wbytes, full);
         if (staged)
           bulk_g2s(stage + lay.sc_off + r * lay.sc_row, p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row,
                    (uint32_t)scbytes, full);
       }
+      // activations of this window: wbytes / 16 blocks of E elements per row, 16 bytes (8 elements) per copy
+      const int slots = (wbytes >> 4) * NQ;
+      const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
+      for (int c = pl; c < M * slots; c += PL) {
+        const int m = c / slots, sl = c - m * slots;
+        cp_async16(stage + lay.x_off + m * lay.x_row + swizzle_slot<NQ>(sl) * 16,
+                   xg + (size_t)m * p.ldx * 2 + xbyte0 + (size_t)sl * 16);
+      }
+      cp_async_arrive_noinc(full);
       if (++s == p.stages) { s = 0; parity ^= 1u; }
     }
   }
@@ -261,7 +267,9 @@ __device__ __forceinline__ void producer(const Params& p, unsigned char* smem, u
 // ---------------------------------------------------------------------------------------------------------------
 // Consumer bodies: one 16-byte block of each of R rows times M activation rows. `wrow` points at the block of the
 // warp's first row in the stage, rows are `wstride` bytes apart; `xs` at the stage's activations.
-// acc[r][m] = (even chain, odd chain).
+// acc[r][m] = (even chain, odd chain). With few activation rows (FEW) the activations of the block are converted
+// once and held while the rows stream past; otherwise the rows' weights are decoded once and held while the
+// activation rows stream past. Per (row, m) both issue the same operations in the same order.
 
 template <int NQ>
 struct XOffsets {   // byte offsets of the lane's NQ swizzled slots inside one step of one activation row
@@ -272,38 +280,75 @@ struct XOffsets {   // byte offsets of the lane's NQ swizzled slots inside one s
   }
 };
 
-template <int M, int R, typename XT>
+template <typename XT>
+__device__ __forceinline__ void load_x8(const unsigned char* p, float2 (&x)[4]) {   // 8 activations -> 4 FP32 pairs
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  x[0] = pair_to_f32(v.x, XT());
+  x[1] = pair_to_f32(v.y, XT());
+  x[2] = pair_to_f32(v.z, XT());
+  x[3] = pair_to_f32(v.w, XT());
+}
+__device__ __forceinline__ float2 fma4(const float2 (&w)[4], const float2 (&x)[4], float2 a) {
+  a = __ffma2_rn(w[0], x[0], a);
+  a = __ffma2_rn(w[1], x[1], a);
+  a = __ffma2_rn(w[2], x[2], a);
+  return __ffma2_rn(w[3], x[3], a);
+}
+
+// 8 weights of a sub-block as 4 FP32 pairs.
+__device__ __forceinline__ void decode_bf16(const uint4& v, float2 (&w)[4]) {
+  w[0] = pair_to_f32(v.x, __nv_bfloat16());
+  w[1] = pair_to_f32(v.y, __nv_bfloat16());
+  w[2] = pair_to_f32(v.z, __nv_bfloat16());
+  w[3] = pair_to_f32(v.w, __nv_bfloat16());
+}
+__device__ __forceinline__ void decode_e4m3(uint32_t a, uint32_t b, float2 (&w)[4]) {
+  w[0] = e4m3x2_to_f32(a);
+  w[1] = e4m3x2_to_f32(a >> 16);
+  w[2] = e4m3x2_to_f32(b);
+  w[3] = e4m3x2_to_f32(b >> 16);
+}
+__device__ __forceinline__ void decode_e2m1(uint32_t a, float2 (&w)[4]) {
+  w[0] = e2m1x2_to_f32(a);
+  w[1] = e2m1x2_to_f32(a >> 8);
+  w[2] = e2m1x2_to_f32(a >> 16);
+  w[3] = e2m1x2_to_f32(a >> 24);
+}
+
+template <bool FEW, int M, int R, typename XT>
 __device__ __forceinline__ void body_bf16(const unsigned char* wrow, int wstride, int nr, const unsigned char* xs,
                                           int x_row, float2 (&acc)[R][M]) {
-  float2 wf[R][4];
+  uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const uint4 v = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
-    wf[r][0] = pair_to_f32(v.x, __nv_bfloat16());
-    wf[r][1] = pair_to_f32(v.y, __nv_bfloat16());
-    wf[r][2] = pair_to_f32(v.z, __nv_bfloat16());
-    wf[r][3] = pair_to_f32(v.w, __nv_bfloat16());
-  }
+  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+  if constexpr (FEW) {
+    float2 xf[M][4];
 #pragma unroll
-  for (int m = 0; m < M; ++m) {
-    const uint4 v = *reinterpret_cast<const uint4*>(xs + m * x_row);
-    const float2 x0 = pair_to_f32(v.x, XT()), x1 = pair_to_f32(v.y, XT()), x2 = pair_to_f32(v.z, XT()),
-                 x3 = pair_to_f32(v.w, XT());
+    for (int m = 0; m < M; ++m) load_x8<XT>(xs + m * x_row, xf[m]);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      float2 a = acc[r][m];
-      a = __ffma2_rn(wf[r][0], x0, a);
-      a = __ffma2_rn(wf[r][1], x1, a);
-      a = __ffma2_rn(wf[r][2], x2, a);
-      a = __ffma2_rn(wf[r][3], x3, a);
-      acc[r][m] = a;
+      float2 wf[4];
+      decode_bf16(wv[r], wf);
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = fma4(wf, xf[m], acc[r][m]);
+    }
+  } else {
+    float2 wf[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) decode_bf16(wv[r], wf[r]);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float2 xf[4];
+      load_x8<XT>(xs + m * x_row, xf);
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r][m] = fma4(wf[r], xf, acc[r][m]);
     }
   }
 }
 
 // FP8 / MXFP8: the block is two sub-blocks of 8 weights (words 0-1, words 2-3). `sc` holds the MXFP8 scale of each
-// row's block (unused for FP8).
-template <bool MX, int M, int R, typename XT>
+// row's block (unused for FP8): every weight is multiplied by it (exact: a power of two).
+template <bool FEW, bool MX, int M, int R, typename XT>
 __device__ __forceinline__ void body_fp8(const unsigned char* wrow, int wstride, int nr, const float (&sc)[R],
                                          const unsigned char* xs, int x_row, const XOffsets<2>& xo,
                                          float2 (&acc)[R][M]) {
@@ -312,41 +357,57 @@ __device__ __forceinline__ void body_fp8(const unsigned char* wrow, int wstride,
   for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    float2 wf[R][4];
+    if constexpr (FEW) {
+      float2 xf[M][4];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const uint32_t a = j ? wv[r].z : wv[r].x, b = j ? wv[r].w : wv[r].y;
-      wf[r][0] = e4m3x2_to_f32(a);
-      wf[r][1] = e4m3x2_to_f32(a >> 16);
-      wf[r][2] = e4m3x2_to_f32(b);
-      wf[r][3] = e4m3x2_to_f32(b >> 16);
-      if (MX) {
-        const float2 s2 = make_float2(sc[r], sc[r]);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) wf[r][q] = __fmul2_rn(wf[r][q], s2);
-      }
-    }
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const uint4 v = *reinterpret_cast<const uint4*>(xs + m * x_row + xo.off[j]);
-      const float2 x0 = pair_to_f32(v.x, XT()), x1 = pair_to_f32(v.y, XT()), x2 = pair_to_f32(v.z, XT()),
-                   x3 = pair_to_f32(v.w, XT());
+      for (int m = 0; m < M; ++m) load_x8<XT>(xs + m * x_row + xo.off[j], xf[m]);
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        float2 a = acc[r][m];
-        a = __ffma2_rn(wf[r][0], x0, a);
-        a = __ffma2_rn(wf[r][1], x1, a);
-        a = __ffma2_rn(wf[r][2], x2, a);
-        a = __ffma2_rn(wf[r][3], x3, a);
-        acc[r][m] = a;
+        float2 wf[4];
+        decode_e4m3(j ? wv[r].z : wv[r].x, j ? wv[r].w : wv[r].y, wf);
+        if (MX) {
+          const float2 s2 = make_float2(sc[r], sc[r]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) wf[q] = __fmul2_rn(wf[q], s2);
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = fma4(wf, xf[m], acc[r][m]);
+      }
+    } else {
+      float2 wf[R][4];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        decode_e4m3(j ? wv[r].z : wv[r].x, j ? wv[r].w : wv[r].y, wf[r]);
+        if (MX) {
+          const float2 s2 = make_float2(sc[r], sc[r]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) wf[r][q] = __fmul2_rn(wf[r][q], s2);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float2 xf[4];
+        load_x8<XT>(xs + m * x_row + xo.off[j], xf);
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r][m] = fma4(wf[r], xf, acc[r][m]);
       }
     }
   }
 }
 
 // NVFP4: the block is 32 codes = two scale blocks of 16 (words 0-1 with scale .x, words 2-3 with scale .y). The 16
-// products of a scale block are summed first (two chains of 8), then acc = fma(scale, partial, acc).
-template <int M, int R, typename XT>
+// products of a scale block are summed first (two chains of 8, started by a multiply), then acc = fma(scale,
+// partial, acc).
+__device__ __forceinline__ float2 dot16(const float2 (&wa)[4], const float2 (&wb)[4], const float2 (&xa)[4],
+                                        const float2 (&xb)[4]) {
+  float2 part = __fmul2_rn(wa[0], xa[0]);
+  part = __ffma2_rn(wa[1], xa[1], part);
+  part = __ffma2_rn(wa[2], xa[2], part);
+  part = __ffma2_rn(wa[3], xa[3], part);
+  return fma4(wb, xb, part);
+}
+
+template <bool FEW, int M, int R, typename XT>
 __device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, int wstride, int nr, const float2 (&sc)[R],
                                            const unsigned char* xs, int x_row, const XOffsets<4>& xo,
                                            float2 (&acc)[R][M]) {
@@ -355,46 +416,108 @@ __device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, int wstrid
   for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    float2 wf[R][8];
+    if constexpr (FEW) {
+      float2 xa[M][4], xb[M][4];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const uint32_t a = h ? wv[r].z : wv[r].x, b = h ? wv[r].w : wv[r].y;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        wf[r][q] = e2m1x2_to_f32(a >> (8 * q));
-        wf[r][4 + q] = e2m1x2_to_f32(b >> (8 * q));
+      for (int m = 0; m < M; ++m) {
+        load_x8<XT>(xs + m * x_row + xo.off[2 * h], xa[m]);
+        load_x8<XT>(xs + m * x_row + xo.off[2 * h + 1], xb[m]);
       }
-    }
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-      const uint4 u = *reinterpret_cast<const uint4*>(xs + m * x_row + xo.off[2 * h]);
-      const uint4 v = *reinterpret_cast<const uint4*>(xs + m * x_row + xo.off[2 * h + 1]);
-      float2 xf[8];
-      xf[0] = pair_to_f32(u.x, XT()); xf[1] = pair_to_f32(u.y, XT());
-      xf[2] = pair_to_f32(u.z, XT()); xf[3] = pair_to_f32(u.w, XT());
-      xf[4] = pair_to_f32(v.x, XT()); xf[5] = pair_to_f32(v.y, XT());
-      xf[6] = pair_to_f32(v.z, XT()); xf[7] = pair_to_f32(v.w, XT());
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        float2 part = __fmul2_rn(wf[r][0], xf[0]);
-#pragma unroll
-        for (int q = 1; q < 8; ++q) part = __ffma2_rn(wf[r][q], xf[q], part);
+        float2 wa[4], wb[4];
+        decode_e2m1(h ? wv[r].z : wv[r].x, wa);
+        decode_e2m1(h ? wv[r].w : wv[r].y, wb);
         const float s = h ? sc[r].y : sc[r].x;
-        acc[r][m] = __ffma2_rn(make_float2(s, s), part, acc[r][m]);
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+          acc[r][m] = __ffma2_rn(make_float2(s, s), dot16(wa, wb, xa[m], xb[m]), acc[r][m]);
+      }
+    } else {
+      float2 wa[R][4], wb[R][4];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        decode_e2m1(h ? wv[r].z : wv[r].x, wa[r]);
+        decode_e2m1(h ? wv[r].w : wv[r].y, wb[r]);
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float2 xa[4], xb[4];
+        load_x8<XT>(xs + m * x_row + xo.off[2 * h], xa);
+        load_x8<XT>(xs + m * x_row + xo.off[2 * h + 1], xb);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float s = h ? sc[r].y : sc[r].x;
+          acc[r][m] = __ffma2_rn(make_float2(s, s), dot16(wa[r], wb[r], xa, xb), acc[r][m]);
+        }
       }
     }
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Lane reduction of V values per lane at once: the xor-shuffle tree 16, 8, 4, 2, 1 of every value, with the values
+// split between the two partners at each level so that a level costs one shuffle per value pair instead of one per
+// value. For each value the additions are those of the plain tree, pair by pair (a + b is commutative in IEEE
+// arithmetic), so the bits are the plain tree's. After the last level value v's total sits in lane (v % 32),
+// slot v / 32.
+template <int V, int OFFSET, int NOUT>
+struct LaneReduce {
+  static constexpr int H = (V + 1) / 2;   // values kept per lane after this level
+  __device__ __forceinline__ static void run(float (&val)[V], int lane, float (&out)[NOUT]) {
+    if constexpr (V == 1) {
+      float v = val[0];
+#pragma unroll
+      for (int o = OFFSET; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      out[0] = v;
+    } else if constexpr (OFFSET == 0) {
+      static_assert(V <= NOUT, "lane reduction output too small");
+#pragma unroll
+      for (int i = 0; i < V; ++i) out[i] = val[i];
+    } else {
+      // lanes with the OFFSET bit clear keep values [0, H) and send [H, V); the others keep [H, V) and send [0, H)
+      const bool upper = (lane & OFFSET) != 0;
+      float keep[H];
+#pragma unroll
+      for (int i = 0; i < H; ++i) {
+        const bool has_hi = H + i < V;
+        const float lo = val[i], hi = has_hi ? val[H + i] : 0.0f;
+        const float got = __shfl_xor_sync(0xffffffffu, upper ? lo : hi, OFFSET);
+        // a value without a partner slot (odd V) is finished by the lower lanes; the upper lanes carry a zero there
+        keep[i] = (upper ? hi : lo) + (has_hi || !upper ? got : 0.0f);
+      }
+      LaneReduce<H, OFFSET / 2, NOUT>::run(keep, lane, out);
+    }
+  }
+};
+
+// Which of the V values lane `lane` holds in output slot `slot` after LaneReduce<V, 16, .> (-1: none).
+template <int V>
+__device__ __forceinline__ int lane_value(int lane, int slot) {
+  int size = V, real = V, base = 0;   // entries [0, real) of this lane's array are values base, base + 1, ...
+  for (int o = 16; o > 0; o >>= 1) {
+    if (size == 1) return (real == 1 && slot == 0 && (lane & (2 * o - 1)) == 0) ? base : -1;
+    const int h = (size + 1) / 2;
+    if (lane & o) {
+      base += h;
+      real = real > h ? real - h : 0;
+    } else {
+      real = real < h ? real : h;
+    }
+    size = h;
+  }
+  return slot < real ? base + slot : -1;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // One tile for one consumer warp holding up to R rows (nr of them real).
 
-template <int FMT, int M, int R, typename XT>
-__device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, const StageLayout<FMT, M>& lay,
+template <int FMT, int M, int R, typename XT, int CW>
+__device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk, const StageLayout<FMT, M, CW>& lay,
                                              unsigned char* smem, uint32_t full0, uint32_t empty0,
-                                             volatile int* abort_flag, int row0, int nr, int& s,
-                                             uint32_t& parity) {
+                                             volatile int* abort_flag, int row0, int nr, int& s, uint32_t& parity) {
   constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
+  constexpr bool FEW = few_rows(FMT, M);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const XOffsets<NQ> xo(lane);
   float2 acc[R][M];
@@ -402,8 +525,8 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, co
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[r][m] = make_float2(0.f, 0.f);
-  const int wstride = kConsumerWarps * lay.w_row;       // the warp's rows are kConsumerWarps tile rows apart
-  const int scstride = kConsumerWarps * lay.sc_row;
+  const int wstride = CW * lay.w_row;       // the warp's rows are CW tile rows apart
+  const int scstride = CW * lay.sc_row;
 
   for (int win = 0; win < wk.nwin; ++win) {
     if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;
@@ -417,10 +540,10 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, co
           const unsigned char* wrow = stage + warp * lay.w_row + st * kStepBytes + lane * 16;
           const unsigned char* xs = stage + lay.x_off + st * (64 * E);
           if constexpr (FMT == FMT_BF16) {
-            body_bf16<M, R, XT>(wrow, wstride, nr, xs + lane * 16, lay.x_row, acc);
+            body_bf16<FEW, M, R, XT>(wrow, wstride, nr, xs + lane * 16, lay.x_row, acc);
           } else if constexpr (FMT == FMT_FP8) {
             float none[R];
-            body_fp8<false, M, R, XT>(wrow, wstride, nr, none, xs, lay.x_row, xo, acc);
+            body_fp8<FEW, false, M, R, XT>(wrow, wstride, nr, none, xs, lay.x_row, xo, acc);
           } else if constexpr (FMT == FMT_MXFP8) {
             float sc[R];
 #pragma unroll
@@ -430,10 +553,10 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, co
               if (p.scale_mode == SCALES_STAGED)
                 e = stage[lay.sc_off + warp * lay.sc_row + rr * scstride + st * SCB + (lane >> 1)];
               else
-                e = __ldg(p.scales + (size_t)(row0 + warp + kConsumerWarps * rr) * p.scale_row_bytes + (blk >> 1));
+                e = __ldg(p.scales + (size_t)(row0 + warp + CW * rr) * p.scale_row_bytes + (blk >> 1));
               sc[r] = e8m0_to_f32(e);
             }
-            body_fp8<true, M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
+            body_fp8<FEW, true, M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
           } else {
             float2 sc[R];
 #pragma unroll
@@ -444,14 +567,14 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, co
                 e = *reinterpret_cast<const uint16_t*>(stage + lay.sc_off + warp * lay.sc_row + rr * scstride +
                                                        st * SCB + lane * 2);
               } else {
-                const int n = row0 + warp + kConsumerWarps * rr;
+                const int n = row0 + warp + CW * rr;
                 const size_t off = p.scale_mode == SCALES_BLOCKED ? tiled_scale_offset(n, blk * 2, p.ct)
                                                                    : (size_t)n * p.scale_row_bytes + blk * 2;
                 e = __ldg(reinterpret_cast<const uint16_t*>(p.scales + off));
               }
               sc[r] = e4m3x2_to_f32(e);
             }
-            body_nvfp4<M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
+            body_nvfp4<FEW, M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
           }
         }
       }
@@ -461,18 +584,24 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, co
     if (++s == p.stages) { s = 0; parity ^= 1u; }
   }
 
-  // the two chains, then the lanes: xor-shuffle tree 16, 8, 4, 2, 1; scale once; round once
+  // the two chains, then the lanes (xor-shuffle tree 16, 8, 4, 2, 1); scale once; round once
+  constexpr int V = R * M;
+  float val[V];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    if (r < nr) {
-      const int n = row0 + warp + kConsumerWarps * r;
-      const float scale = p.row_scale ? __ldg(p.row_scale + n) : 1.0f;
+  for (int r = 0; r < R; ++r)
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float v = acc[r][m].x + acc[r][m].y;
+    for (int m = 0; m < M; ++m) val[r * M + m] = acc[r][m].x + acc[r][m].y;
+  float total[(V + 31) / 32];
+  LaneReduce<V, 16, (V + 31) / 32>::run(val, lane, total);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, p.row_scale ? v * scale : v);
+  for (int i = 0; i < (V + 31) / 32; ++i) {
+    const int v = lane_value<V>(lane, i);
+    if (v >= 0) {
+      const int r = v / M, m = v - r * M;
+      if (r < nr) {
+        const int n = row0 + warp + CW * r;
+        const float sum = total[i];
+        store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, p.row_scale ? sum * __ldg(p.row_scale + n) : sum);
       }
     }
   }
@@ -480,16 +609,17 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk& wk, co
 }
 
 template <int FMT, int M, typename XT>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ Params p) {
+__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, 1)
+    gemv_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int RMAX = rows_max(FMT, M);
+  constexpr int RMAX = rows_max(FMT, M), CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
   const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full0 + 8u * s, 33);                    // 32 cp.async completions + the expect_tx arrival
-      mbar_init(empty0 + 8u * s, kConsumerWarps);
+      mbar_init(full0 + 8u * s, 32 * PW + 1);           // the producers' cp.async arrivals + the expect_tx arrival
+      mbar_init(empty0 + 8u * s, CW);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -498,30 +628,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
   __syncthreads();
 
   const int warp = threadIdx.x >> 5;
-  if (warp == kConsumerWarps) {
-    producer<FMT, M>(p, smem, full0, empty0, abort_flag);
+  if (warp >= CW) {
+    producer<FMT, M, CW, PW>(p, smem, full0, empty0, abort_flag, (int)threadIdx.x - CW * 32);
   } else {
-    const Walk wk(p);
-    const StageLayout<FMT, M> lay(p);
+    const Walk<CW> wk(p);
+    const StageLayout<FMT, M, CW> lay(p);
     int s = 0;
     uint32_t parity = 0;
     bool ok = true;
     for (int t = 0; t < wk.ntiles && ok; ++t) {
       const int row0 = wk.lo + t * wk.tile_rows;
       const int rows = min(wk.tile_rows, wk.hi - row0);
-      const int nr = rows > warp ? (rows - warp + kConsumerWarps - 1) / kConsumerWarps : 0;
-      if (RMAX >= 8 && nr > 4)
-        ok = consume_tile<FMT, M, (RMAX >= 8 ? 8 : RMAX), XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
-                                                                    parity);
-      else if (RMAX >= 4 && nr > 2)
-        ok = consume_tile<FMT, M, (RMAX >= 4 ? 4 : RMAX), XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
-                                                                    parity);
-      else if (RMAX >= 2 && nr > 1)
-        ok = consume_tile<FMT, M, 2, XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
-                                                                    parity);
+      const int nr = rows > warp ? (rows - warp + CW - 1) / CW : 0;
+      if (nr > 2)
+        ok = consume_tile<FMT, M, RMAX, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
+      else if (nr > 1)
+        ok = consume_tile<FMT, M, 2, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
       else
-        ok = consume_tile<FMT, M, 1, XT>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s,
-                                                                    parity);
+        ok = consume_tile<FMT, M, 1, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
     }
     if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
   }

@@ -8,7 +8,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _OPS_LIB = os.path.join(_HERE, "_decode_gemv_b200.so")
 
 if not os.path.exists(_OPS_LIB):
-    raise ImportError(f"{_OPS_LIB} is missing: build it with `python -m crit_kernels_b200.build` "
+    raise ImportError(f"{_OPS_LIB} is missing: build it with `python -m crit_kernels_b200.builder` "
                       "(there is no fallback path)")
 torch.ops.load_library(_OPS_LIB)
 ops = torch.ops._decode_gemv_b200

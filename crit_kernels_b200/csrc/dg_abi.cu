@@ -28,6 +28,35 @@ struct DeviceState {
   int sms = 0;
   int* status = nullptr;
 };
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against libcuda.
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult found;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &found) != cudaSuccess ||
+        found != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<EncodeTiled>(ptr);
+  }();
+  return fn;
+}
+
+// A map over `rows` rows of `row_bytes` bytes (a multiple of 16) as 8-byte elements, box = box_rows x box_bytes.
+bool encode_rows(CUtensorMap* map, const void* base, int rows, int row_bytes, int box_rows, int box_bytes) {
+  EncodeTiled fn = encode_tiled();
+  if (!fn || row_bytes % 16 || box_bytes % 16 || box_bytes / 8 > 256 || box_rows > 256 || box_rows < 1) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(box_bytes / 8), (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 DeviceState g_devices[kMaxDevices];
 
 const void* const* const kTables[] = {dg_table_bf16,       dg_table_fp8_bf16,   dg_table_fp8_f16,  dg_table_mxfp8_bf16,
@@ -92,18 +121,19 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
     rmax = force_rows;
   p.rows_per_warp = per_warp < rmax ? per_warp : rmax;
   const int rows_cap = cw * p.rows_per_warp;
-  const int w_step = rows_cap * (dg::kStepBytes + f.scb);
+  const int w_step = rows_cap * (dg::kStepBytes + f.scb);   // sizing estimate; the exact stage size is below
   const int x_step = M * 64 * f.e;
   const int row_steps = ceil_div(p.nblk, 32);
   int steps = ceil_div(24576, w_step);
   if (steps < 2) steps = 2;
-  if (steps > 8) steps = 8;
+  if (steps > 4) steps = 4;   // a tensor-copy box is at most 256 eight-byte elements (2 KB) wide
   if (steps > row_steps) steps = row_steps;
   while (steps > 1 && steps * x_step > 32768) --steps;
   if (force_steps >= 1) steps = force_steps < row_steps ? force_steps : row_steps;
   if (steps < 1) steps = 1;
   p.steps = steps;
-  p.stage_bytes = (steps * (w_step + x_step) + 127) & ~127;
+  p.stage_bytes = (steps * (rows_cap * dg::kStepBytes + x_step) +
+                   p.rows_per_warp * dg::scale_group_bytes(cw, steps, f.scb) + 127) & ~127;
   int stages = (dg::kSmemLimit - dg::kSmemHeader) / p.stage_bytes;
   if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return false;
@@ -120,6 +150,12 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   int ctas = 0, smem = 0;
   if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
   p.status = st->status;
+  // Tensor maps for the 2-D copies of full row groups; without them every row travels as a 1-D bulk copy.
+  const int cw = dg::consumer_warps(fmt, M);
+  const int win_bytes = p.steps * dg::kStepBytes;
+  p.use_2d = p.N >= cw && encode_rows(&p.tmap_w, p.w, p.N, p.row_bytes, cw, win_bytes);
+  if (p.use_2d && p.scale_mode == dg::SCALES_STAGED)
+    p.use_2d = encode_rows(&p.tmap_sc, p.scales, p.N, p.scale_row_bytes, cw, p.steps * kFormats[fmt].scb);
   void* args[] = {&p};
   const int threads = 32 * (dg::consumer_warps(fmt, M) + dg::producer_warps(fmt, M));
   const cudaError_t e = cudaLaunchKernel(kTables[table][M - 1], dim3(ctas), dim3(threads), args, smem, stream);

@@ -23,6 +23,7 @@
 // scales multiply a 16-element partial sum (one fma per block and row instead of one multiply per weight).
 #pragma once
 
+#include <cuda.h>   // CUtensorMap (type only; the driver entry point is looked up at run time)
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
@@ -53,13 +54,15 @@ template <> struct Format<FMT_MXFP8> { static constexpr int E = 16, SCB = 16; };
 template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 
 // CTA shape per (format, M): a speed choice, never a row's bits.
-//   few activation rows   the kernel is HBM-bound: 12 consumer + 4 producer warps (128 registers each). One warp
-//                         issues a bulk copy every ~60 clocks, so four producers keep 1 KB copies above the HBM rate.
+//   few activation rows   the kernel is HBM-bound: 14 consumer + 2 producer warps (128 registers each), as many
+//                         warps as the register file gives, to hide shared-memory and conversion latencies.
 //   more activation rows  the kernel is FP32-FMA-bound: 6 consumer + 2 producer warps, 255 registers each for the
 //                         accumulators of 3-4 rows x M.
+// One warp issues a 1-D bulk copy only every ~60 clocks, so full groups of rows travel as one 2-D tensor copy and
+// only a tile's ragged remainder as per-row copies.
 __host__ __device__ constexpr bool few_rows(int fmt, int m) { return fmt == FMT_NVFP4 ? m <= 2 : m <= 4; }
-__host__ __device__ constexpr int consumer_warps(int fmt, int m) { return few_rows(fmt, m) ? 12 : 6; }
-__host__ __device__ constexpr int producer_warps(int fmt, int m) { return few_rows(fmt, m) ? 4 : 2; }
+__host__ __device__ constexpr int consumer_warps(int fmt, int m) { return few_rows(fmt, m) ? 14 : 6; }
+__host__ __device__ constexpr int producer_warps(int fmt, int m) { return 2; }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }
 
@@ -81,6 +84,11 @@ struct Params {
   int stages;                // ring depth
   int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
+  int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
+  // Tensor maps over the weight rows and the row-major scale rows as 8-byte elements: box = (consumer warps) rows
+  // x one window. Rows are 16-byte multiples apart, which the encoder requires.
+  alignas(64) CUtensorMap tmap_w;
+  alignas(64) CUtensorMap tmap_sc;
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -133,6 +141,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// 2-D tiled tensor copy: box of the tensor map at element column x, row y.
+__device__ __forceinline__ void tensor_g2s(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
                : "memory");
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -193,18 +207,24 @@ struct Walk {
   }
 };
 
-// Shared-memory stage: [weights rows_cap x win_bytes][scales rows_cap x steps*SCB][x M x steps*64*E bytes].
+// Bytes of the scales of one group of `cw` rows in a stage, padded to the 128 bytes a tensor copy's destination
+// must be aligned to.
+__host__ __device__ constexpr int scale_group_bytes(int cw, int steps, int scb) { return (cw * steps * scb + 127) & ~127; }
+
+// Shared-memory stage: [weights rows_cap x win_bytes][scales: r groups of CW rows x steps*SCB, each group padded to
+// 128 bytes][x M x steps*64*E bytes]. Tile row t = w + CW * g is row w of group g.
 template <int FMT, int M, int CW>
 struct StageLayout {
   static constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB;
-  int w_row, sc_row, x_row, sc_off, x_off;
+  int w_row, sc_row, sc_group, x_row, sc_off, x_off;
   __device__ __forceinline__ StageLayout(const Params& p) {
     const int rows_cap = CW * p.rows_per_warp;
     w_row = p.steps * kStepBytes;
     sc_row = p.steps * SCB;
+    sc_group = scale_group_bytes(CW, p.steps, SCB);
     x_row = p.steps * 64 * E;
     sc_off = rows_cap * w_row;
-    x_off = sc_off + rows_cap * sc_row;
+    x_off = sc_off + p.rows_per_warp * sc_group;
   }
 };
 
@@ -240,15 +260,26 @@ __device__ __forceinline__ void producer(const Params& p, unsigned char* smem, u
       const int byte0 = win * wk.win_bytes;
       const int wbytes = min(wk.win_bytes, p.row_bytes - byte0);
       const int scbytes = staged ? (wbytes * SCB) >> 9 : 0;
-      // One arrival carries the byte count of every bulk copy of the stage; completions may land before it (the
-      // phase cannot end while this arrival and the producers' cp.async arrivals are outstanding).
-      if (pl == 0) mbar_arrive_expect_tx(full, (uint32_t)rows * (uint32_t)(wbytes + scbytes));
-      for (int r = pl; r < rows; r += PL) {
+      // Full groups of CW rows travel as one 2-D tensor copy each (always the whole box: columns past the row's end
+      // are zero-filled and still counted), the remainder as one 1-D bulk copy per row. One arrival carries the byte
+      // count of them all; completions may land before it (the phase cannot end while this arrival and the
+      // producers' cp.async arrivals are outstanding).
+      const int boxes = p.use_2d ? rows / CW : 0;
+      const int box_rows = boxes * CW;
+      if (pl == 0)
+        mbar_arrive_expect_tx(full, (uint32_t)box_rows * (uint32_t)(lay.w_row + (staged ? lay.sc_row : 0)) +
+                                        (uint32_t)(rows - box_rows) * (uint32_t)(wbytes + scbytes));
+      if (pl < boxes) {
+        tensor_g2s(stage + pl * CW * lay.w_row, &p.tmap_w, byte0 >> 3, row0 + pl * CW, full);
+        if (staged)
+          tensor_g2s(stage + lay.sc_off + pl * lay.sc_group, &p.tmap_sc, (win * lay.sc_row) >> 3, row0 + pl * CW, full);
+      }
+      for (int r = box_rows + pl; r < rows; r += PL) {
         const size_t n = (size_t)(row0 + r);
         bulk_g2s(stage + r * lay.w_row, p.w + n * p.row_bytes + byte0, (uint32_t)wbytes, full);
         if (staged)
-          bulk_g2s(stage + lay.sc_off + r * lay.sc_row, p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row,
-                   (uint32_t)scbytes, full);
+          bulk_g2s(stage + lay.sc_off + (r / CW) * lay.sc_group + (r % CW) * lay.sc_row,
+                   p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row, (uint32_t)scbytes, full);
       }
       // activations of this window: wbytes / 16 blocks of E elements per row, 16 bytes (8 elements) per copy
       const int slots = (wbytes >> 4) * NQ;
@@ -526,7 +557,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[r][m] = make_float2(0.f, 0.f);
   const int wstride = CW * lay.w_row;       // the warp's rows are CW tile rows apart
-  const int scstride = CW * lay.sc_row;
+  const int scstride = lay.sc_group;     // and one scale group apart
 
   for (int win = 0; win < wk.nwin; ++win) {
     if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;

@@ -98,10 +98,10 @@ constexpr FormatInfo kFormats[4] = {{8, 0}, {16, 0}, {16, 16}, {32, 64}};
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Launch shape: a speed choice from (format, M, N, K, SM count) only; no row's bits depend on it.
-//   CTAs            one per SM, fewer when the matrix has under one row per consumer warp and SM
+//   CTAs            one per SM, fewer when the matrix has under four rows per SM
 //   rows per warp   the most the kernel holds (rows_max), less when a CTA's range is short
-//   steps           512-byte steps per ring stage: at least two (bulk copies of 1 KB or more keep the copy issue
-//                   rate off the critical path), more when a tile has few rows (about 24 KB of weights per stage),
+//   steps           512-byte steps per ring stage: at least two (1 KB of every row per stage: 512-byte pieces cost
+//                   DRAM efficiency and per-row bulk copies are issue-limited), up to four when a tile has few rows;
 //                   activations under 32 KB per stage
 //   stages          as many as fit in shared memory, at most kMaxStages
 bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem) {
@@ -110,7 +110,7 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   const long long row_bits = (long long)K * 128 / f.e;   // 16 bytes per e elements
   p.row_bytes = (int)(row_bits / 8);
   p.nblk = p.row_bytes / 16;
-  ctas = sms < ceil_div(N, cw) ? sms : ceil_div(N, cw);
+  ctas = sms < ceil_div(N, 4) ? sms : ceil_div(N, 4);
   const int rows_per_cta = ceil_div(N, ctas);
   const int per_warp = ceil_div(rows_per_cta, cw);
   int rmax = dg::rows_max(fmt, M);
@@ -124,7 +124,7 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   const int w_step = rows_cap * (dg::kStepBytes + f.scb);   // sizing estimate; the exact stage size is below
   const int x_step = M * 64 * f.e;
   const int row_steps = ceil_div(p.nblk, 32);
-  int steps = ceil_div(24576, w_step);
+  int steps = ceil_div(32768, w_step);
   if (steps < 2) steps = 2;
   if (steps > 4) steps = 4;   // a tensor-copy box is at most 256 eight-byte elements (2 KB) wide
   if (steps > row_steps) steps = row_steps;
@@ -150,6 +150,8 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   int ctas = 0, smem = 0;
   if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
   p.status = st->status;
+  static const bool skip = std::getenv("DG_DEBUG_SKIP") != nullptr;
+  p.debug_skip = skip;
   // Tensor maps for the 2-D copies of full row groups; without them every row travels as a 1-D bulk copy.
   const int cw = dg::consumer_warps(fmt, M);
   const int win_bytes = p.steps * dg::kStepBytes;

@@ -53,15 +53,23 @@ template <> struct Format<FMT_FP8>   { static constexpr int E = 16, SCB = 0;  };
 template <> struct Format<FMT_MXFP8> { static constexpr int E = 16, SCB = 16; };   // step of one row
 template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 
-// CTA shape per (format, M): a speed choice, never a row's bits.
-//   few activation rows   the kernel is HBM-bound: 14 consumer + 2 producer warps (128 registers each), as many
-//                         warps as the register file gives, to hide shared-memory and conversion latencies.
-//   more activation rows  the kernel is FP32-FMA-bound: 6 consumer + 2 producer warps, 255 registers each for the
-//                         accumulators of 3-4 rows x M.
+// CTA shape per (format, M): a speed choice, never a row's bits. Register need decides it: the accumulators take
+// 2 * rows * M registers and the held operand (activations or decoded weights) 8-16 per activation row or weight row.
+//   class 0   M small: the kernel is HBM-bound. 14 consumer + 2 producer warps (128 registers each): as many warps
+//             as the register file gives, to hide shared-memory and conversion latencies.
+//   class 1   M medium: 10 consumer + 2 producer warps (168 registers each).
+//   class 2   M large: the kernel is FP32-FMA-bound. 6 consumer + 2 producer warps, 255 registers each.
+// Classes 0 and 1 hold the converted activations of a block and stream the rows past them; class 2 holds the rows'
+// decoded weights and streams the activation rows.
 // One warp issues a 1-D bulk copy only every ~60 clocks, so full groups of rows travel as one 2-D tensor copy and
 // only a tile's ragged remainder as per-row copies.
-__host__ __device__ constexpr bool few_rows(int fmt, int m) { return fmt == FMT_NVFP4 ? m <= 2 : m <= 4; }
-__host__ __device__ constexpr int consumer_warps(int fmt, int m) { return few_rows(fmt, m) ? 14 : 6; }
+__host__ __device__ constexpr int shape_class(int fmt, int m) {
+  return fmt == FMT_NVFP4 ? (m <= 2 ? 0 : m <= 4 ? 1 : 2) : (m <= 4 ? 0 : m <= 8 ? 1 : 2);
+}
+__host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class(fmt, m) < 2; }
+__host__ __device__ constexpr int consumer_warps(int fmt, int m) {
+  return shape_class(fmt, m) == 0 ? 14 : shape_class(fmt, m) == 1 ? 10 : 6;
+}
 __host__ __device__ constexpr int producer_warps(int fmt, int m) { return 2; }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }
@@ -85,6 +93,7 @@ struct Params {
   int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
+  int debug_skip;            // tuning aid: consumers skip the arithmetic (results are then meaningless)
   // Tensor maps over the weight rows and the row-major scale rows as 8-byte elements: box = (consumer warps) rows
   // x one window. Rows are 16-byte multiples apart, which the encoder requires.
   alignas(64) CUtensorMap tmap_w;
@@ -567,7 +576,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
       const int nsteps = min(p.steps, (p.nblk - blk0 + 31) >> 5);
       for (int st = 0; st < nsteps; ++st) {
         const int blk = blk0 + st * 32 + lane;
-        if (blk < p.nblk) {
+        if (blk < p.nblk && !p.debug_skip) {
           const unsigned char* wrow = stage + warp * lay.w_row + st * kStepBytes + lane * 16;
           const unsigned char* xs = stage + lay.x_off + st * (64 * E);
           if constexpr (FMT == FMT_BF16) {

@@ -10,7 +10,7 @@ The reference has no multi-GPU code; this module is new work on top of the op su
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
@@ -43,15 +43,15 @@ class StackRun:
         self.stack, self.m = stack, m
         dev = stack.device
         g = torch.Generator().manual_seed(4242 + m)
-        self.x_host = {role: torch.randn(m, k, generator=g).to(torch.bfloat16).pin_memory()
-                       for role, k, _ in stack.roles}
+        pin = (lambda t: t.pin_memory()) if dev.type == "cuda" else (lambda t: t)
+        self.x_host = {role: pin(torch.randn(m, k, generator=g).to(torch.bfloat16)) for role, k, _ in stack.roles}
         self.x = {role: t.to(dev) for role, t in self.x_host.items()}
         self.shard = {role: torch.empty(m, n // stack.world, dtype=torch.bfloat16, device=dev)
                       for role, _, n in stack.roles}
         self.full = {role: torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16, device=dev)
                      for role, _, n in stack.roles}
         last = stack.roles[-1][0]
-        self.out_host = torch.empty_like(self.full[last], device="cpu").pin_memory()
+        self.out_host = pin(torch.empty_like(self.full[last], device="cpu"))
         self.h2d_bytes = sum(t.numel() * 2 for t in self.x_host.values())
         self.d2h_bytes = self.out_host.numel() * 2
         self.kernel_launches = len(stack.projections)
@@ -63,8 +63,7 @@ class StackRun:
         for p in st.projections:
             st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
             if st.world > 1:
-                dist.all_gather_into_tensor(self.full[p.role].view(-1, self.shard[p.role].shape[1]),
-                                            self.shard[p.role], group=st.group)
+                st.gather(self.full[p.role], self.shard[p.role])
                 if keep is not None:
                     keep.append(self.full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone())
             elif keep is not None:
@@ -104,14 +103,18 @@ class ShardedStack:
     world: int
     device: torch.device
     group: object = None
-    kernel: object = field(default_factory=get_kernel)
+    kernel: object = None
 
     @property
     def gather_kind(self):
         return "none (1 GPU)" if self.world == 1 else "NCCL all_gather_into_tensor after every GEMV, inside the graph"
 
+    def gather(self, full, shard):
+        """full [P][M][N/P] <- every rank's shard [M][N/P]."""
+        dist.all_gather_into_tensor(full.view(-1, shard.shape[1]), shard, group=self.group)
+
     @classmethod
-    def random(cls, layers, roles, rank, world, device, seed=0, group=None):
+    def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None):
         """`layers` x `roles` projections; every rank draws the same full matrix from the same seed and keeps its
         rows, so the shards of all ranks together are exactly the matrix a single GPU would hold."""
         projections = []
@@ -125,7 +128,7 @@ class ShardedStack:
                 projections.append(Projection(role, k, n, codes[lo:hi].clone(), scales[lo:hi].clone(),
                                               inverse[lo:hi].clone()))
                 del codes, scales, inverse
-        return cls(projections, tuple(roles), rank, world, device, group)
+        return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel())
 
     def capture(self, m):
         return StackRun(self, m).capture()
@@ -134,5 +137,6 @@ class ShardedStack:
         """Eager pass; returns every projection's gathered output (for tests)."""
         keep = []
         StackRun(self, m).eager(keep)
-        torch.cuda.synchronize()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
         return keep

@@ -1,0 +1,45 @@
+"""The column-sharded NVFP4 stack on 2 (and 4) GPUs: the gathered outputs are bit-identical to the single-GPU outputs
+for every projection and M, eager and from the captured graph. Needs at least two GPUs (skipped otherwise); ranks are
+child processes over NCCL on 127.0.0.1."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROLES = (("qkv", 1024, 1280), ("o", 1024, 1024), ("gate_up", 1024, 7168), ("down", 3584, 1024))
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from crit_kernels_b200 import stack as stk
+        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=5)
+        whole = stk.ShardedStack.random(2, ROLES, 0, 1, dev, seed=5)
+        for m in (1, 8, 16):
+            got, want = sharded.run(m), whole.run(m)
+            for i, (g, w) in enumerate(zip(got, want)):
+                assert torch.equal(g.view(torch.int16), w.view(torch.int16)), (m, i)
+            run = sharded.capture(m)
+            run.replay()
+            torch.cuda.synchronize()
+            last = run.full["down"].permute(1, 0, 2).reshape(m, -1)
+            assert torch.equal(last, want[-1])
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_stack_reproduces_the_single_gpu_bits(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_worker, args=(world, 29531 + world, results), nprocs=world, join=True)
+        assert dict(results) == {r: "ok" for r in range(world)}

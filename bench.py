@@ -303,6 +303,24 @@ def run_case(args):
     print(json.dumps({"case": args.case, "us": ms * 1e3, "GBps": nbytes / ms / 1e6, "weight_bytes": nbytes}), flush=True)
 
 
+def leave_distributed():
+    """End of a multi-rank run. destroy_process_group blocks while a CUDA graph that captured the group's collectives
+    is alive (seen on this torch/NCCL build), so the graphs are released first; a timer ends the process anyway
+    should the teardown still not return (the printed line and exit code 0 are what the caller needs)."""
+    import gc
+    import torch.distributed as dist
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    guard = threading.Timer(30.0, lambda: os._exit(0))
+    guard.daemon = True
+    guard.start()
+    dist.destroy_process_group()
+    guard.cancel()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -371,7 +389,7 @@ def main():
 
     if rank != 0:
         if world > 1:
-            torch.distributed.destroy_process_group()
+            leave_distributed()
         return
     value = r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e12
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -388,7 +406,7 @@ def main():
                                           "FP32 dequantise + FP32 matmul with torch on the host"}
     print(json.dumps(line), flush=True)
     if world > 1:
-        torch.distributed.destroy_process_group()
+        leave_distributed()
 
 
 if __name__ == "__main__":

@@ -1,6 +1,7 @@
 """The column-sharded NVFP4 stack on 2 (and 4) GPUs: the gathered outputs are bit-identical to the single-GPU outputs
 for every projection and M, eager and from the captured graph. Needs at least two GPUs (skipped otherwise); ranks are
 child processes over NCCL on 127.0.0.1."""
+import datetime
 import os
 
 import pytest
@@ -16,7 +17,8 @@ def _worker(rank, world, port, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=90))
     try:
         from crit_kernels_b200 import stack as stk
         sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=5)
@@ -30,9 +32,17 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             last = run.full["down"].permute(1, 0, 2).reshape(m, -1)
             assert torch.equal(last, want[-1])
+            del run          # a live graph that captured the group's collectives blocks the group's teardown
         results[rank] = "ok"
+        torch.cuda.synchronize()
+        dist.barrier()
     finally:
+        import threading
+        guard = threading.Timer(30.0, lambda: os._exit(0 if results.get(rank) == "ok" else 1))
+        guard.daemon = True
+        guard.start()
         dist.destroy_process_group()
+        guard.cancel()
 
 
 @pytest.mark.parametrize("world", [2, 4])

@@ -150,8 +150,6 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   int ctas = 0, smem = 0;
   if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
   p.status = st->status;
-  static const bool skip = std::getenv("DG_DEBUG_SKIP") != nullptr;
-  p.debug_skip = skip;
   // Tensor maps for the 2-D copies of full row groups; without them every row travels as a 1-D bulk copy.
   const int cw = dg::consumer_warps(fmt, M);
   const int win_bytes = p.steps * dg::kStepBytes;

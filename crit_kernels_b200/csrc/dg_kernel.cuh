@@ -93,7 +93,6 @@ struct Params {
   int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
-  int debug_skip;            // tuning aid: consumers skip the arithmetic (results are then meaningless)
   // Tensor maps over the weight rows and the row-major scale rows as 8-byte elements: box = (consumer warps) rows
   // x one window. Rows are 16-byte multiples apart, which the encoder requires.
   alignas(64) CUtensorMap tmap_w;
@@ -342,25 +341,49 @@ __device__ __forceinline__ void decode_bf16(const uint4& v, float2 (&w)[4]) {
   w[2] = pair_to_f32(v.z, __nv_bfloat16());
   w[3] = pair_to_f32(v.w, __nv_bfloat16());
 }
+__device__ __forceinline__ float2 half2_bits_to_f32(uint32_t h) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+// The conversions take their packed source from a 16-bit (E4M3 pair) or 8-bit (E2M1 pair) register; unpacking the
+// word in PTX lets the assembler select the sub-word instead of shifting it out first.
 __device__ __forceinline__ void decode_e4m3(uint32_t a, uint32_t b, float2 (&w)[4]) {
-  w[0] = e4m3x2_to_f32(a);
-  w[1] = e4m3x2_to_f32(a >> 16);
-  w[2] = e4m3x2_to_f32(b);
-  w[3] = e4m3x2_to_f32(b >> 16);
+  uint32_t h0, h1, h2, h3;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+      : "=r"(h0), "=r"(h1) : "r"(a));
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+      : "=r"(h2), "=r"(h3) : "r"(b));
+  w[0] = half2_bits_to_f32(h0);
+  w[1] = half2_bits_to_f32(h1);
+  w[2] = half2_bits_to_f32(h2);
+  w[3] = half2_bits_to_f32(h3);
 }
 __device__ __forceinline__ void decode_e2m1(uint32_t a, float2 (&w)[4]) {
-  w[0] = e2m1x2_to_f32(a);
-  w[1] = e2m1x2_to_f32(a >> 8);
-  w[2] = e2m1x2_to_f32(a >> 16);
-  w[3] = e2m1x2_to_f32(a >> 24);
+  uint32_t h0, h1, h2, h3;
+  asm("{\n\t.reg .b8 c0, c1, c2, c3;\n\t"
+      "mov.b32 {c0, c1, c2, c3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, c0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, c1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, c2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, c3;\n\t}"
+      : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3) : "r"(a));
+  w[0] = half2_bits_to_f32(h0);
+  w[1] = half2_bits_to_f32(h1);
+  w[2] = half2_bits_to_f32(h2);
+  w[3] = half2_bits_to_f32(h3);
 }
 
 template <bool FEW, int M, int R, typename XT>
-__device__ __forceinline__ void body_bf16(const unsigned char* wrow, int wstride, int nr, const unsigned char* xs,
+__device__ __forceinline__ void body_bf16(const unsigned char* wrow, const int (&woff)[R], const unsigned char* xs,
                                           int x_row, float2 (&acc)[R][M]) {
   uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + woff[r]);
   if constexpr (FEW) {
     float2 xf[M][4];
 #pragma unroll
@@ -389,12 +412,12 @@ __device__ __forceinline__ void body_bf16(const unsigned char* wrow, int wstride
 // FP8 / MXFP8: the block is two sub-blocks of 8 weights (words 0-1, words 2-3). `sc` holds the MXFP8 scale of each
 // row's block (unused for FP8): every weight is multiplied by it (exact: a power of two).
 template <bool FEW, bool MX, int M, int R, typename XT>
-__device__ __forceinline__ void body_fp8(const unsigned char* wrow, int wstride, int nr, const float (&sc)[R],
+__device__ __forceinline__ void body_fp8(const unsigned char* wrow, const int (&woff)[R], const float (&sc)[R],
                                          const unsigned char* xs, int x_row, const XOffsets<2>& xo,
                                          float2 (&acc)[R][M]) {
   uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + woff[r]);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     if constexpr (FEW) {
@@ -448,12 +471,12 @@ __device__ __forceinline__ float2 dot16(const float2 (&wa)[4], const float2 (&wb
 }
 
 template <bool FEW, int M, int R, typename XT>
-__device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, int wstride, int nr, const float2 (&sc)[R],
+__device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, const int (&woff)[R], const float2 (&sc)[R],
                                            const unsigned char* xs, int x_row, const XOffsets<4>& xo,
                                            float2 (&acc)[R][M]) {
   uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + min(r, nr - 1) * wstride);
+  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + woff[r]);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if constexpr (FEW) {
@@ -565,8 +588,16 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
   for (int r = 0; r < R; ++r)
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[r][m] = make_float2(0.f, 0.f);
-  const int wstride = CW * lay.w_row;       // the warp's rows are CW tile rows apart
-  const int scstride = lay.sc_group;     // and one scale group apart
+  // Offsets of the warp's rows inside a stage (rows are CW tile rows and one scale group apart); rows the warp does
+  // not have alias its last real row (their sums are discarded).
+  int woff[R], scoff[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int rr = min(r, max(nr, 1) - 1);
+    woff[r] = (warp + CW * rr) * lay.w_row + lane * 16;
+    scoff[r] = lay.sc_off + warp * lay.sc_row + rr * lay.sc_group;
+  }
+  const bool staged = SCB != 0 && p.scale_mode == SCALES_STAGED;
 
   for (int win = 0; win < wk.nwin; ++win) {
     if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;
@@ -576,45 +607,43 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
       const int nsteps = min(p.steps, (p.nblk - blk0 + 31) >> 5);
       for (int st = 0; st < nsteps; ++st) {
         const int blk = blk0 + st * 32 + lane;
-        if (blk < p.nblk && !p.debug_skip) {
-          const unsigned char* wrow = stage + warp * lay.w_row + st * kStepBytes + lane * 16;
+        if (blk < p.nblk) {
+          const unsigned char* wrow = stage + st * kStepBytes;
           const unsigned char* xs = stage + lay.x_off + st * (64 * E);
           if constexpr (FMT == FMT_BF16) {
-            body_bf16<FEW, M, R, XT>(wrow, wstride, nr, xs + lane * 16, lay.x_row, acc);
+            body_bf16<FEW, M, R, XT>(wrow, woff, xs + lane * 16, lay.x_row, acc);
           } else if constexpr (FMT == FMT_FP8) {
             float none[R];
-            body_fp8<FEW, false, M, R, XT>(wrow, wstride, nr, none, xs, lay.x_row, xo, acc);
+            body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, lay.x_row, xo, acc);
           } else if constexpr (FMT == FMT_MXFP8) {
             float sc[R];
+            if (staged) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              const int rr = min(r, nr - 1);
-              uint32_t e;
-              if (p.scale_mode == SCALES_STAGED)
-                e = stage[lay.sc_off + warp * lay.sc_row + rr * scstride + st * SCB + (lane >> 1)];
-              else
-                e = __ldg(p.scales + (size_t)(row0 + warp + CW * rr) * p.scale_row_bytes + (blk >> 1));
-              sc[r] = e8m0_to_f32(e);
+              for (int r = 0; r < R; ++r) sc[r] = e8m0_to_f32(stage[scoff[r] + st * SCB + (lane >> 1)]);
+            } else {
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                const int n = row0 + warp + CW * min(r, nr - 1);
+                sc[r] = e8m0_to_f32(__ldg(p.scales + (size_t)n * p.scale_row_bytes + (blk >> 1)));
+              }
             }
-            body_fp8<FEW, true, M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
+            body_fp8<FEW, true, M, R, XT>(wrow, woff, sc, xs, lay.x_row, xo, acc);
           } else {
             float2 sc[R];
+            if (staged) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              const int rr = min(r, nr - 1);
-              uint32_t e;
-              if (p.scale_mode == SCALES_STAGED) {
-                e = *reinterpret_cast<const uint16_t*>(stage + lay.sc_off + warp * lay.sc_row + rr * scstride +
-                                                       st * SCB + lane * 2);
-              } else {
-                const int n = row0 + warp + CW * rr;
+              for (int r = 0; r < R; ++r)
+                sc[r] = e4m3x2_to_f32(*reinterpret_cast<const uint16_t*>(stage + scoff[r] + st * SCB + lane * 2));
+            } else {
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                const int n = row0 + warp + CW * min(r, nr - 1);
                 const size_t off = p.scale_mode == SCALES_BLOCKED ? tiled_scale_offset(n, blk * 2, p.ct)
                                                                    : (size_t)n * p.scale_row_bytes + blk * 2;
-                e = __ldg(reinterpret_cast<const uint16_t*>(p.scales + off));
+                sc[r] = e4m3x2_to_f32(__ldg(reinterpret_cast<const uint16_t*>(p.scales + off)));
               }
-              sc[r] = e4m3x2_to_f32(e);
             }
-            body_nvfp4<FEW, M, R, XT>(wrow, wstride, nr, sc, xs, lay.x_row, xo, acc);
+            body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, lay.x_row, xo, acc);
           }
         }
       }

@@ -55,9 +55,10 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 
 // CTA shape per (format, M): a speed choice, never a row's bits. Register need decides it: the accumulators take
 // 2 * rows * M registers and the held operand (activations or decoded weights) 8-16 per activation row or weight row.
-//   class 0   M small: the kernel is HBM-bound. 14 consumer + 2 producer warps (128 registers each): as many warps
-//             as the register file gives, to hide shared-memory and conversion latencies.
-//   class 1   M medium: 10 consumer + 2 producer warps (168 registers each).
+//   class 0   M small: the kernel is HBM-bound. 12 consumer + 4 producer warps (128 registers each): as many warps
+//             as the register file gives, to hide shared-memory and conversion latencies; every SM sub-partition
+//             hosts the same number of consumers.
+//   class 1   M medium: 8 consumer + 4 producer warps (168 registers each).
 //   class 2   M large: the kernel is FP32-FMA-bound. 6 consumer + 2 producer warps, 255 registers each.
 // Classes 0 and 1 hold the converted activations of a block and stream the rows past them; class 2 holds the rows'
 // decoded weights and streams the activation rows.
@@ -68,9 +69,9 @@ __host__ __device__ constexpr int shape_class(int fmt, int m) {
 }
 __host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class(fmt, m) < 2; }
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? 14 : shape_class(fmt, m) == 1 ? 10 : 6;
+  return shape_class(fmt, m) == 0 ? 12 : shape_class(fmt, m) == 1 ? 8 : 6;
 }
-__host__ __device__ constexpr int producer_warps(int fmt, int m) { return 2; }
+__host__ __device__ constexpr int producer_warps(int fmt, int m) { return shape_class(fmt, m) == 2 ? 2 : 4; }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }
 
@@ -168,7 +169,8 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 // Element conversions. All exact.
 
 __device__ __forceinline__ float2 pair_to_f32(uint32_t v, __nv_bfloat16) {   // two BF16 -> two FP32
-  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+  // byte permute for the low element: keeps the shift off the FMA pipe, which the packed FMAs need
+  return make_float2(__uint_as_float(__byte_perm(v, 0u, 0x1044u)), __uint_as_float(v & 0xffff0000u));
 }
 __device__ __forceinline__ float2 pair_to_f32(uint32_t v, __half) {          // two FP16 -> two FP32
   return __half22float2(*reinterpret_cast<const __half2*>(&v));
@@ -292,10 +294,11 @@ __device__ __forceinline__ void producer(const Params& p, unsigned char* smem, u
       // activations of this window: wbytes / 16 blocks of E elements per row, 16 bytes (8 elements) per copy
       const int slots = (wbytes >> 4) * NQ;
       const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
-      for (int c = pl; c < M * slots; c += PL) {
-        const int m = c / slots, sl = c - m * slots;
-        cp_async16(stage + lay.x_off + m * lay.x_row + swizzle_slot<NQ>(sl) * 16,
-                   xg + (size_t)m * p.ldx * 2 + xbyte0 + (size_t)sl * 16);
+#pragma unroll 1
+      for (int m = 0; m < M; ++m) {
+        const uint32_t dst = stage + lay.x_off + m * lay.x_row;
+        const unsigned char* src = xg + (size_t)m * p.ldx * 2 + xbyte0;
+        for (int sl = pl; sl < slots; sl += PL) cp_async16(dst + swizzle_slot<NQ>(sl) * 16, src + (size_t)sl * 16);
       }
       cp_async_arrive_noinc(full);
       if (++s == p.stages) { s = 0; parity ^= 1u; }
@@ -720,8 +723,10 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
   }
   // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
   // memory is handed to the next one (bounded sleep, error path only).
-  if (*abort_flag)
+  if (*abort_flag) {
+#pragma unroll 1
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
 }
 
 }  // namespace dg

@@ -241,7 +241,7 @@ def run_stack(args, dev, rank, world, ms=STACK_MS, layers=None):
     from crit_kernels_b200 import stack as stk
     from oracle import workloads as wl
     layers = layers or wl.STACK_LAYERS
-    model = stk.ShardedStack.random(layers, wl.STACK_ROLES, rank, world, dev, seed=99)
+    model = stk.ShardedStack.random(layers, wl.STACK_ROLES, rank, world, dev, seed=99, gather=args.gather)
     runs = {m: model.capture(m) for m in ms}
     barrier = (lambda: dist.barrier()) if world > 1 else None
 
@@ -329,6 +329,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "c1", "stack"])
     ap.add_argument("--layers", type=int, default=None, help="stack depth (default 80)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="stack workload on N > 1 GPUs: all-gather fused into the GEMV epilogue, or NCCL per GEMV")
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
                     help="run `--steps` calls of one GEMV (fmt in bf16, fp8, mxfp8, nvfp4) and exit: the small case "
                          "profilers capture")

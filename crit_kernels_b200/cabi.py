@@ -11,6 +11,8 @@ _PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libdeco
 _p, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)
 SIGNATURES = {
     "dg_enqueue_nvfp4": (_i, [_p, _i, _i, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dg_enqueue_nvfp4_allgather": (_i, [_p, _i, _i, _p, _p, _i, _p, ctypes.POINTER(_p), ctypes.POINTER(_p), _i, _i, _i,
+                                        _i, _i, _i, _i, _p]),
     "dg_enqueue_fp8": (_i, [_p, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_hardware_decode": (_i, []),

@@ -185,6 +185,32 @@ int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes
   return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
 }
 
+int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
+                               int blocked, const float* inverse, void* const* peer_out, void* const* peer_flags,
+                               int world, int rank, int slot, int out_kind, int M, int N, int K, void* stream) {
+  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return (int)cudaErrorInvalidValue;
+  if (!x || !codes || !scales || !inverse || !peer_out || !peer_flags || ldx % 8 || !aligned(x, 16) ||
+      !aligned(codes, 16) || !aligned(scales, 2) || !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1) ||
+      world < 2 || world > dg::kMaxRanks || rank < 0 || rank >= world || (slot != 0 && slot != 1))
+    return (int)cudaErrorInvalidValue;
+  Params p{};
+  p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse; p.ldo = N;
+  p.out_kind = out_kind == 0 ? dg::OUT_F32 : (x_is_bf16 ? dg::OUT_BF16 : dg::OUT_F16);
+  p.N = N; p.K = K;
+  p.scale_row_bytes = K / 16;
+  p.ct = blocked ? (K / 16 + 3) / 4 : 0;
+  p.scale_mode = blocked ? dg::SCALES_BLOCKED
+                         : (K % 256 == 0 && aligned(scales, 16)) ? dg::SCALES_STAGED : dg::SCALES_DIRECT;
+  p.world = world; p.rank = rank; p.gather_slot = slot;
+  for (int q = 0; q < world; ++q) {
+    if (!peer_out[q] || !peer_flags[q] || !aligned(peer_flags[q], 4)) return (int)cudaErrorInvalidValue;
+    p.peer_out[q] = peer_out[q];
+    p.peer_flag[q] = static_cast<unsigned int*>(peer_flags[q]);
+  }
+  p.out = peer_out[rank];
+  return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
+}
+
 int dg_enqueue_fp8(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const float* row_scale,
                    const uint8_t* mx_scale, void* out, int ldo, int out_kind, int M, int N, int K, void* stream) {
   if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 16 || K % 16 || (mx_scale && K % 32) || (!row_scale == !mx_scale))

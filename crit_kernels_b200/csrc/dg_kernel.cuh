@@ -46,6 +46,8 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // bounded waits: a
 // status word bits written on a wait that ran out (never expected; the host can read the word)
 constexpr int kStatusProducerTimeout = 1;
 constexpr int kStatusConsumerTimeout = 2;
+constexpr int kStatusGatherTimeout = 4;
+constexpr int kMaxRanks = 8;
 
 template <int FMT> struct Format;
 template <> struct Format<FMT_BF16>  { static constexpr int E = 8,  SCB = 0;  };   // elements / scale bytes per
@@ -94,6 +96,13 @@ struct Params {
   int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
+  // All-gather epilogue (world > 1): this rank's [M][N] results are written into slot `rank` of every rank's
+  // [world][M][N] buffer (peer_out[q], peer-mapped addresses), every consumer warp then adds 1 to counter
+  // `gather_slot` of every rank's flag pair (peer_flag[q]) and one thread of this rank waits until its own counter
+  // holds world * CTAs * consumer warps, then clears it: when the kernel ends, every rank's data has landed here.
+  int world, rank, gather_slot;
+  void* peer_out[kMaxRanks];
+  unsigned int* peer_flag[kMaxRanks];
   // Tensor maps over the weight rows and the row-major scale rows as 8-byte elements: box = (consumer warps) rows
   // x one window. Rows are 16-byte multiples apart, which the encoder requires.
   alignas(64) CUtensorMap tmap_w;
@@ -673,11 +682,43 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
       if (r < nr) {
         const int n = row0 + warp + CW * r;
         const float sum = total[i];
-        store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, p.row_scale ? sum * __ldg(p.row_scale + n) : sum);
+        const float result = p.row_scale ? sum * __ldg(p.row_scale + n) : sum;
+        if (p.world <= 1) {
+          store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, result);
+        } else {
+          const size_t idx = ((size_t)p.rank * M + m) * p.ldo + n;
+          for (int q = 0; q < p.world; ++q) store_out(p.peer_out[q], p.out_kind, idx, result);
+        }
       }
     }
   }
   return true;
+}
+
+// End of a consumer warp in an all-gather launch: publish the warp's peer stores, count the warp in on every rank,
+// and (one thread of the rank) wait, bounded, for every rank's warps.
+template <int CW>
+__device__ __forceinline__ void gather_finish(const Params& p, volatile int* abort_flag) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncwarp();
+  __threadfence_system();
+  if (lane == 0)
+    for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.gather_slot, 1u);
+  if (blockIdx.x == 0 && warp == 0 && lane == 0) {
+    volatile unsigned int* mine = p.peer_flag[p.rank] + p.gather_slot;
+    const unsigned int want = (unsigned int)p.world * gridDim.x * CW;
+    const unsigned long long start = global_ns();
+    bool done = false;
+    for (unsigned int i = 1; !done; ++i) {
+      unsigned int seen;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+      done = seen >= want;
+      if (!done && (i & 63u) == 0u && (*abort_flag || global_ns() - start > kWaitLimitNs)) break;
+    }
+    if (done) atomicSub_system(const_cast<unsigned int*>(mine), want);
+    else if (p.status) atomicOr(p.status, kStatusGatherTimeout);
+    __threadfence_system();
+  }
 }
 
 template <int FMT, int M, typename XT>
@@ -720,6 +761,7 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
         ok = consume_tile<FMT, M, 1, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
     }
     if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
+    if (p.world > 1) gather_finish<CW>(p, abort_flag);
   }
   // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
   // memory is handed to the next one (bounded sleep, error path only).

@@ -2,7 +2,10 @@
 
 Each projection's output columns (rows of the [N][K] weight matrix) are split evenly over the ranks of one node: rank r
 holds rows [r*N/P, (r+1)*N/P) of codes, block scales and inverse scales (contiguous slices, no repacking), multiplies
-the full activations by its slice, and an all-gather over NVLink assembles the [M][N] result on every rank. The K
+the full activations by its slice, and an all-gather over NVLink assembles the [M][N] result on every rank: either
+fused into the GEMV kernel's epilogue (gather="fused": every rank's gathered buffer lives in symmetric memory, the
+kernel stores its results straight into all of them over NVLink and ends when every rank's results have landed here)
+or as one NCCL all_gather_into_tensor after each GEMV (gather="nccl", the baseline). The K
 dimension is never split: a row's sum is computed by one GPU in the order it has on a single GPU, so the gathered
 output is bit-identical to the unsharded one (tests/test_stack_*.py).
 
@@ -10,6 +13,7 @@ The reference has no multi-GPU code; this module is new work on top of the op su
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 
 import torch
@@ -36,6 +40,30 @@ def random_nvfp4(n, k, device, generator):
     return codes, scales.view(torch.uint8), torch.ones(n, device=device)
 
 
+class FusedGatherBuffers:
+    """Symmetric memory for one StackRun: every role's gathered buffer [P][M][N/P] and the pair of arrival counters,
+    in one arena allocated with torch's symmetric-memory allocator and mapped into every rank's address space."""
+
+    def __init__(self, stack, m):
+        import torch.distributed._symmetric_memory as symm
+        world = stack.world
+        offsets, total = {}, 256                       # the counters live in the first 256 bytes
+        for role, _, n in stack.roles:
+            offsets[role] = total
+            total += (world * m * (n // world) * 2 + 255) // 256 * 256
+        self.arena = symm.empty(total, dtype=torch.uint8, device=stack.device)
+        self.arena.zero_()
+        self.handle = symm.rendezvous(self.arena, stack.group if stack.group is not None else dist.group.WORLD)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        array = ctypes.c_void_p * world
+        self.flag_ptrs = array(*ptrs)
+        self.out_ptrs = {role: array(*[p + off for p in ptrs]) for role, off in offsets.items()}
+        self.full = {role: self.arena[off:off + world * m * (n // world) * 2].view(torch.bfloat16)
+                     .view(world, m, n // world) for (role, _, n), off in zip(stack.roles, offsets.values())}
+        torch.cuda.synchronize()
+        dist.barrier(group=stack.group)                # every rank's counters are zero before anyone signals
+
+
 class StackRun:
     """One captured pass over the stack at a fixed row count M."""
 
@@ -48,8 +76,11 @@ class StackRun:
         self.x = {role: t.to(dev) for role, t in self.x_host.items()}
         self.shard = {role: torch.empty(m, n // stack.world, dtype=torch.bfloat16, device=dev)
                       for role, _, n in stack.roles}
-        self.full = {role: torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16, device=dev)
-                     for role, _, n in stack.roles}
+        self.fused = FusedGatherBuffers(stack, m) if stack.world > 1 and stack.gather == "fused" else None
+        self.calls = 0
+        self.full = self.fused.full if self.fused else {
+            role: torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16, device=dev)
+            for role, _, n in stack.roles}
         last = stack.roles[-1][0]
         self.out_host = pin(torch.empty_like(self.full[last], device="cpu"))
         self.h2d_bytes = sum(t.numel() * 2 for t in self.x_host.values())
@@ -61,13 +92,30 @@ class StackRun:
         """Runs the pass on the current stream; `keep` collects every projection's gathered [M][N] output."""
         st = self.stack
         for p in st.projections:
-            st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
+            if self.fused:
+                self._gemv_allgather(p)
+            else:
+                st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
+                if st.world > 1:
+                    st.nccl_gather(self.full[p.role], self.shard[p.role])
             if st.world > 1:
-                st.gather(self.full[p.role], self.shard[p.role])
                 if keep is not None:
                     keep.append(self.full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone())
             elif keep is not None:
                 keep.append(self.shard[p.role].clone())
+
+    def _gemv_allgather(self, p):
+        """The GEMV with the all-gather in its epilogue (C ABI dg_enqueue_nvfp4_allgather) on the current stream."""
+        from . import cabi
+        st, x = self.stack, self.x[p.role]
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+        code = cabi.load().dg_enqueue_nvfp4_allgather(
+            ptr(x), x.stride(0), 1, ptr(p.codes), ptr(p.scales), 0, ptr(p.inverse), self.fused.out_ptrs[p.role],
+            self.fused.flag_ptrs, st.world, st.rank, self.calls & 1, 1, self.m, p.codes.shape[0], p.k,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if code:
+            raise RuntimeError(f"dg_enqueue_nvfp4_allgather: cudaError {code}")
+        self.calls += 1
 
     def capture(self):
         side = torch.cuda.Stream(device=self.stack.device)
@@ -104,17 +152,22 @@ class ShardedStack:
     device: torch.device
     group: object = None
     kernel: object = None
+    gather: str = "fused"       # "fused": all-gather in the GEMV epilogue over symmetric memory; "nccl": NCCL per GEMV
 
     @property
     def gather_kind(self):
-        return "none (1 GPU)" if self.world == 1 else "NCCL all_gather_into_tensor after every GEMV, inside the graph"
+        if self.world == 1:
+            return "none (1 GPU)"
+        if self.gather == "fused":
+            return "fused into the GEMV epilogue: peer stores into every rank's symmetric buffer + arrival counters"
+        return "NCCL all_gather_into_tensor after every GEMV, inside the graph"
 
-    def gather(self, full, shard):
+    def nccl_gather(self, full, shard):
         """full [P][M][N/P] <- every rank's shard [M][N/P]."""
         dist.all_gather_into_tensor(full.view(-1, shard.shape[1]), shard, group=self.group)
 
     @classmethod
-    def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None):
+    def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None, gather="fused"):
         """`layers` x `roles` projections; every rank draws the same full matrix from the same seed and keeps its
         rows, so the shards of all ranks together are exactly the matrix a single GPU would hold."""
         projections = []
@@ -128,7 +181,9 @@ class ShardedStack:
                 projections.append(Projection(role, k, n, codes[lo:hi].clone(), scales[lo:hi].clone(),
                                               inverse[lo:hi].clone()))
                 del codes, scales, inverse
-        return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel())
+        if gather not in ("fused", "nccl"):
+            raise ValueError(f"gather must be 'fused' or 'nccl', not {gather!r}")
+        return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel(), gather)
 
     def capture(self, m):
         return StackRun(self, m).capture()

@@ -37,6 +37,20 @@ extern "C" {
 DG_API int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales, int blocked,
                      const float* inverse, void* out, int ldo, int out_kind, int M, int N, int K, void* stream);
 
+/* NVFP4 GEMV of one rank's slice of the output columns with the all-gather fused into the kernel's epilogue. No
+ * counterpart in the reference (it has no multi-GPU code); it is the column-sharded stack's replacement for "GEMV,
+ * then NCCL all-gather". All `world` ranks (2..8, one GPU each, peers mapped into each other's address space) call
+ * it in the same order with the same M, N (rows of this rank's slice), K and slot. peer_out[q] is rank q's gathered
+ * buffer [world][M][N] (FP32 or x's type) and peer_flags[q] rank q's pair of zero-initialised 32-bit counters, both
+ * as addresses valid on the calling device (host arrays of `world` pointers, read during the call). The kernel stores
+ * its [M][N] results into slot `rank` of every rank's buffer, counts itself in on every rank's counter `slot`, and
+ * ends only when every rank's results have arrived in this rank's buffer (bounded wait: dg_take_status bit 2 on
+ * time-out). Consecutive calls alternate slot 0 and 1. */
+DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
+                                      int blocked, const float* inverse, void* const* peer_out,
+                                      void* const* peer_flags, int world, int rank, int slot, int out_kind, int M,
+                                      int N, int K, void* stream);
+
 /* FP8 E4M3 W8A16. Replaces enqueue_gemv_fp8 (decode_gemv.h:34-36, decode_gemv.cu:402-417).
  * Exactly one of row_scale ([N] FP32: out = row_scale[n] * sum) and mx_scale ([N][K/32] E8M0 bytes, MXFP8:
  * each weight times 2^(e - 127)) is non-null. codes [N][K] bytes on 16 bytes, K % 16 == 0 (32 for MXFP8), K >= 16. */

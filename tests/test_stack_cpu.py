@@ -27,7 +27,7 @@ def _worker(rank, world, port, results):
     try:
         from crit_kernels_b200 import stack as stk
         dev = torch.device("cpu")
-        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=3, kernel=HostKernel())
+        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=3, kernel=HostKernel(), gather="nccl")
         whole = stk.ShardedStack.random(2, ROLES, 0, 1, dev, seed=3, kernel=HostKernel())
         assert sharded.projections[0].codes.shape[0] == ROLES[0][2] // world
         lo = rank * ROLES[0][2] // world

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 ROLES = (("qkv", 1024, 1280), ("o", 1024, 1024), ("gate_up", 1024, 7168), ("down", 3584, 1024))
 
 
-def _worker(rank, world, port, results):
+def _worker(rank, world, port, gather, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
@@ -21,7 +21,7 @@ def _worker(rank, world, port, results):
                             timeout=datetime.timedelta(seconds=90))
     try:
         from crit_kernels_b200 import stack as stk
-        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=5)
+        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=5, gather=gather)
         whole = stk.ShardedStack.random(2, ROLES, 0, 1, dev, seed=5)
         for m in (1, 8, 16):
             got, want = sharded.run(m), whole.run(m)
@@ -32,6 +32,9 @@ def _worker(rank, world, port, results):
             torch.cuda.synchronize()
             last = run.full["down"].permute(1, 0, 2).reshape(m, -1)
             assert torch.equal(last, want[-1])
+            run.replay()                                     # a second replay: the arrival counters were re-armed
+            torch.cuda.synchronize()
+            assert torch.equal(run.full["down"].permute(1, 0, 2).reshape(m, -1), want[-1])
             del run          # a live graph that captured the group's collectives blocks the group's teardown
         results[rank] = "ok"
         torch.cuda.synchronize()
@@ -45,11 +48,13 @@ def _worker(rank, world, port, results):
         guard.cancel()
 
 
+@pytest.mark.parametrize("gather", ["fused", "nccl"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_sharded_stack_reproduces_the_single_gpu_bits(world):
+def test_sharded_stack_reproduces_the_single_gpu_bits(world, gather):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as manager:
         results = manager.dict()
-        mp.spawn(_worker, args=(world, 29531 + world, results), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, 29531 + world + (10 if gather == "fused" else 0), gather, results), nprocs=world,
+                 join=True)
         assert dict(results) == {r: "ok" for r in range(world)}

@@ -191,7 +191,7 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
   if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return (int)cudaErrorInvalidValue;
   if (!x || !codes || !scales || !inverse || !peer_out || !peer_flags || ldx % 8 || !aligned(x, 16) ||
       !aligned(codes, 16) || !aligned(scales, 2) || !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1) ||
-      world < 2 || world > dg::kMaxRanks || rank < 0 || rank >= world || (slot != 0 && slot != 1))
+      world < 1 || world > dg::kMaxRanks || rank < 0 || rank >= world || (slot != 0 && slot != 1))
     return (int)cudaErrorInvalidValue;
   Params p{};
   p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse; p.ldo = N;

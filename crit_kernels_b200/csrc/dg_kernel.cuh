@@ -96,7 +96,7 @@ struct Params {
   int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
-  // All-gather epilogue (world > 1): this rank's [M][N] results are written into slot `rank` of every rank's
+  // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results are written into slot `rank` of every rank's
   // [world][M][N] buffer (peer_out[q], peer-mapped addresses), every consumer warp then adds 1 to counter
   // `gather_slot` of every rank's flag pair (peer_flag[q]) and one thread of this rank waits until its own counter
   // holds world * CTAs * consumer warps, then clears it: when the kernel ends, every rank's data has landed here.
@@ -683,7 +683,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
         const int n = row0 + warp + CW * r;
         const float sum = total[i];
         const float result = p.row_scale ? sum * __ldg(p.row_scale + n) : sum;
-        if (p.world <= 1) {
+        if (p.world < 1) {
           store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, result);
         } else {
           const size_t idx = ((size_t)p.rank * M + m) * p.ldo + n;
@@ -761,7 +761,7 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
         ok = consume_tile<FMT, M, 1, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
     }
     if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
-    if (p.world > 1) gather_finish<CW>(p, abort_flag);
+    if (p.world >= 1) gather_finish<CW>(p, abort_flag);
   }
   // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
   // memory is handed to the next one (bounded sleep, error path only).

@@ -39,7 +39,7 @@ DG_API int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t
 
 /* NVFP4 GEMV of one rank's slice of the output columns with the all-gather fused into the kernel's epilogue. No
  * counterpart in the reference (it has no multi-GPU code); it is the column-sharded stack's replacement for "GEMV,
- * then NCCL all-gather". All `world` ranks (2..8, one GPU each, peers mapped into each other's address space) call
+ * then NCCL all-gather". All `world` ranks (1..8, one GPU each, peers mapped into each other's address space) call
  * it in the same order with the same M, N (rows of this rank's slice), K and slot. peer_out[q] is rank q's gathered
  * buffer [world][M][N] (FP32 or x's type) and peer_flags[q] rank q's pair of zero-initialised 32-bit counters, both
  * as addresses valid on the calling device (host arrays of `world` pointers, read during the call). The kernel stores

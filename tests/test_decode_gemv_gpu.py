@@ -287,3 +287,28 @@ def test_no_bounded_wait_ran_out():
     """After everything above, the kernels' error word is clean."""
     from crit_kernels_b200 import cabi
     assert cabi.load().dg_take_status() == 0
+
+
+def test_one_rank_allgather_is_the_plain_gemv():
+    """The all-gather entry point with a single rank: results land in slot 0 of the gathered buffer, bit-identical
+    to the plain GEMV, and the arrival counters are back at zero after every call."""
+    import ctypes
+    from crit_kernels_b200 import cabi
+    n, k, m = 520, 2048, 5
+    c, s, i = cuda(*wl.cfg_nvfp4(n, k))
+    x = wl.activations(m, k).to(dev)
+    want = gemv_abi("nvfp4", x, (c, s, i), torch.bfloat16)
+    full = torch.zeros(1, m, n, dtype=torch.bfloat16, device=dev)
+    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    outs = (ctypes.c_void_p * 1)(full.data_ptr())
+    flag_ptrs = (ctypes.c_void_p * 1)(flags.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for call in range(4):
+        full.zero_()
+        code = cabi.load().dg_enqueue_nvfp4_allgather(ptr(x), x.stride(0), 1, ptr(c), ptr(s), 0, ptr(i), outs, flag_ptrs,
+                                                      1, 0, call & 1, 1, m, n, k, stream)
+        assert code == 0
+        torch.cuda.synchronize()
+        assert torch.equal(full[0], want) and int(flags.abs().sum()) == 0
+    assert cabi.load().dg_take_status() == 0

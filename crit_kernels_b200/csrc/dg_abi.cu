@@ -211,6 +211,51 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
   return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
 }
 
+// ---- the entry point that allocates nothing ---------------------------------------------------------------------
+// Arrival counters for dg_enqueue_nvfp4_allgather_noalloc: DG_NOALLOC_CHANNELS pairs of 32-bit counters that live in
+// the library's image on every GPU that loads it (512 bytes per GPU, held until the process exits), zero when the
+// module is loaded and re-armed to zero by every call that completes. In host code `dg_gather_scratch` is only a
+// handle for the runtime, not a device address: the address a kernel may use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+static __device__ __align__(256) unsigned int dg_gather_scratch[2 * DG_NOALLOC_CHANNELS];
+static unsigned int* g_gather_scratch[kMaxDevices];   // per device, filled by the first call that names the device
+
+static cudaError_t gather_scratch_of(int device, unsigned int** out) {
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!g_gather_scratch[device]) {
+    int previous = 0;
+    cudaError_t e = cudaGetDevice(&previous);
+    if (e == cudaSuccess && previous != device) e = cudaSetDevice(device);
+    void* address = nullptr;
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&address, dg_gather_scratch);
+    if (previous != device) {
+      const cudaError_t back = cudaSetDevice(previous);
+      if (e == cudaSuccess) e = back;
+    }
+    if (e != cudaSuccess) return e;
+    g_gather_scratch[device] = static_cast<unsigned int*>(address);
+  }
+  *out = g_gather_scratch[device];
+  return cudaSuccess;
+}
+
+int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, const uint8_t* codes,
+                                       const uint8_t* scales, int blocked, const float* inverse,
+                                       void* const* peer_out, const int* devices, int world, int rank, int channel,
+                                       int slot, int out_kind, int M, int N, int K, void* stream) {
+  if (!devices || world < 1 || world > dg::kMaxRanks || channel < 0 || channel >= DG_NOALLOC_CHANNELS)
+    return (int)cudaErrorInvalidValue;   // more ranks or channels than the built-in counters cover
+  void* flags[dg::kMaxRanks];
+  for (int q = 0; q < world; ++q) {
+    unsigned int* base = nullptr;
+    const cudaError_t e = gather_scratch_of(devices[q], &base);
+    if (e != cudaSuccess) return (int)e;
+    flags[q] = base + 2 * channel;
+  }
+  return dg_enqueue_nvfp4_allgather(x, ldx, x_is_bf16, codes, scales, blocked, inverse, peer_out, flags, world, rank,
+                                    slot, out_kind, M, N, K, stream);
+}
+
 int dg_enqueue_fp8(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const float* row_scale,
                    const uint8_t* mx_scale, void* out, int ldo, int out_kind, int M, int N, int K, void* stream) {
   if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 16 || K % 16 || (mx_scale && K % 32) || (!row_scale == !mx_scale))

@@ -51,6 +51,33 @@ DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, con
                                       void* const* peer_flags, int world, int rank, int slot, int out_kind, int M,
                                       int N, int K, void* stream);
 
+/* dg_enqueue_nvfp4_allgather for callers that cannot allocate device memory. No counterpart in the reference.
+ *
+ * Who needs it: a serving process that hands all of HBM to its own weight and KV-cache arenas at start-up and has
+ * nothing left for cudaMalloc afterwards; a plugin host or a latency-critical decode loop that forbids allocation
+ * after initialisation because cudaMalloc synchronises the device and can fail; code that only learns it needs the
+ * counters while a stream is being captured. Such callers own the gathered output buffers already, but have no
+ * memory for the arrival counters the fused all-gather needs. Here the counters are DG_NOALLOC_CHANNELS pairs built
+ * into the library (512 bytes on every GPU that loads it, until the process exits); this call and everything under
+ * it calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Arguments as dg_enqueue_nvfp4_allgather, except that instead of peer_flags the caller names the CUDA device
+ * ordinal of every rank (devices[q], host array of `world` ints) and a channel 0 .. DG_NOALLOC_CHANNELS - 1; rank q's
+ * counters are the pair `channel` in device devices[q]'s copy of the library's array, so all ranks must live in
+ * this process (one thread or stream per GPU) with peer access enabled between their devices; world = 1 needs
+ * neither. More than 8 ranks or a channel outside the range is refused with cudaErrorInvalidValue (1): the built-in
+ * counters cover nothing larger.
+ * The first call that names a device looks up that device's array (cudaSetDevice + cudaGetSymbolAddress, then back):
+ * make that first call outside any stream capture.
+ * Every call on a channel shares its two counters, which keep whatever the last call left: a completed call leaves
+ * them zero, and that is the state the next call requires. Two calls on the same channel that overlap on the GPU, or a
+ * call after one that timed out (dg_take_status bit 2), race on the counters; use another channel, or order them. */
+#define DG_NOALLOC_CHANNELS 64
+DG_API int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, const uint8_t* codes,
+                                              const uint8_t* scales, int blocked, const float* inverse,
+                                              void* const* peer_out, const int* devices, int world, int rank,
+                                              int channel, int slot, int out_kind, int M, int N, int K, void* stream);
+
 /* FP8 E4M3 W8A16. Replaces enqueue_gemv_fp8 (decode_gemv.h:34-36, decode_gemv.cu:402-417).
  * Exactly one of row_scale ([N] FP32: out = row_scale[n] * sum) and mx_scale ([N][K/32] E8M0 bytes, MXFP8:
  * each weight times 2^(e - 127)) is non-null. codes [N][K] bytes on 16 bytes, K % 16 == 0 (32 for MXFP8), K >= 16. */

@@ -212,12 +212,12 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
 }
 
 // ---- the entry point that allocates nothing ---------------------------------------------------------------------
-// Arrival counters for dg_enqueue_nvfp4_allgather_noalloc: DG_NOALLOC_CHANNELS pairs of 32-bit counters that live in
-// the library's image on every GPU that loads it (512 bytes per GPU, held until the process exits), zero when the
+// Arrival counters for dg_enqueue_nvfp4_allgather_noalloc: DG_NOALLOC_CHANNELS blocks of four 32-bit counters that live
+// in the library's image on every GPU that loads it (1 KB per GPU, held until the process exits), zero when the
 // module is loaded and re-armed to zero by every call that completes. In host code `dg_gather_scratch` is only a
 // handle for the runtime, not a device address: the address a kernel may use comes from cudaGetSymbolAddress, asked
 // once per device with that device current.
-static __device__ __align__(256) unsigned int dg_gather_scratch[2 * DG_NOALLOC_CHANNELS];
+static __device__ __align__(256) unsigned int dg_gather_scratch[4 * DG_NOALLOC_CHANNELS];
 static unsigned int* g_gather_scratch[kMaxDevices];   // per device, filled by the first call that names the device
 
 static cudaError_t gather_scratch_of(int device, unsigned int** out) {
@@ -250,7 +250,7 @@ int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, co
     unsigned int* base = nullptr;
     const cudaError_t e = gather_scratch_of(devices[q], &base);
     if (e != cudaSuccess) return (int)e;
-    flags[q] = base + 2 * channel;
+    flags[q] = base + 4 * channel;
   }
   return dg_enqueue_nvfp4_allgather(x, ldx, x_is_bf16, codes, scales, blocked, inverse, peer_out, flags, world, rank,
                                     slot, out_kind, M, N, K, stream);

@@ -96,10 +96,11 @@ struct Params {
   int rows_per_warp;         // r: a full tile is (consumer warps) * r rows
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
-  // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results are written into slot `rank` of every rank's
-  // [world][M][N] buffer (peer_out[q], peer-mapped addresses), every consumer warp then adds 1 to counter
-  // `gather_slot` of every rank's flag pair (peer_flag[q]) and one thread of this rank waits until its own counter
-  // holds world * CTAs * consumer warps, then clears it: when the kernel ends, every rank's data has landed here.
+  // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results go into slot `rank` of its own
+  // [world][M][N] buffer; every CTA then copies its rows to the same slot of every other rank's buffer (peer_out[q],
+  // peer-mapped addresses) and counts itself done in word 2 of this rank's counter block; the last CTA adds 1 to
+  // word `gather_slot` (0 or 1) of every rank's block (peer_flag[q]) and waits until its own word holds `world`, then
+  // clears it: when the kernel ends, every rank's data has landed here.
   int world, rank, gather_slot;
   void* peer_out[kMaxRanks];
   unsigned int* peer_flag[kMaxRanks];
@@ -686,8 +687,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
         if (p.world < 1) {
           store_out(p.out, p.out_kind, (size_t)m * p.ldo + n, result);
         } else {
-          const size_t idx = ((size_t)p.rank * M + m) * p.ldo + n;
-          for (int q = 0; q < p.world; ++q) store_out(p.peer_out[q], p.out_kind, idx, result);
+          store_out(p.out, p.out_kind, ((size_t)p.rank * M + m) * p.ldo + n, result);
         }
       }
     }
@@ -695,30 +695,48 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
   return true;
 }
 
-// End of a consumer warp in an all-gather launch: publish the warp's peer stores, count the warp in on every rank,
-// and (one thread of the rank) wait, bounded, for every rank's warps.
-template <int CW>
+// End of the consumer warps of a CTA in an all-gather launch. The CTA's rows [lo, hi) of this rank's slot are
+// complete in the local buffer; all consumer threads copy them, coalesced, into the other ranks' buffers; one thread
+// publishes the copies and counts the CTA done; the rank's last CTA tells every rank and waits, bounded, for all of
+// them.
+template <int M, int CW>
 __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abort_flag) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  __syncwarp();
-  __threadfence_system();
-  if (lane == 0)
-    for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.gather_slot, 1u);
-  if (blockIdx.x == 0 && warp == 0 && lane == 0) {
-    volatile unsigned int* mine = p.peer_flag[p.rank] + p.gather_slot;
-    const unsigned int want = (unsigned int)p.world * gridDim.x * CW;
-    const unsigned long long start = global_ns();
-    bool done = false;
-    for (unsigned int i = 1; !done; ++i) {
-      unsigned int seen;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-      done = seen >= want;
-      if (!done && (i & 63u) == 0u && (*abort_flag || global_ns() - start > kWaitLimitNs)) break;
+  const int tid = threadIdx.x;                       // consumer threads are 0 .. CW * 32 - 1
+  asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+  const int lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
+  const int rows = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x) - lo;
+  const size_t slot0 = (size_t)p.rank * M * p.ldo + lo;
+  for (int q = 0; q < p.world; ++q) {
+    if (q == p.rank) continue;
+    for (int i = tid; i < M * rows; i += CW * 32) {
+      const int m = i / rows, r = i - m * rows;
+      const size_t idx = slot0 + (size_t)m * p.ldo + r;
+      if (p.out_kind == OUT_F32)
+        reinterpret_cast<float*>(p.peer_out[q])[idx] = reinterpret_cast<const float*>(p.out)[idx];
+      else
+        reinterpret_cast<uint16_t*>(p.peer_out[q])[idx] = reinterpret_cast<const uint16_t*>(p.out)[idx];
     }
-    if (done) atomicSub_system(const_cast<unsigned int*>(mine), want);
-    else if (p.status) atomicOr(p.status, kStatusGatherTimeout);
-    __threadfence_system();
   }
+  asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+  if (tid != 0) return;
+  unsigned int* mine = p.peer_flag[p.rank];
+  __threadfence_system();                            // the CTA's copies, before it counts as done
+  if (atomicAdd(mine + 2, 1u) != gridDim.x - 1) return;
+  atomicExch(mine + 2, 0u);                          // last CTA of the rank: re-arm the CTA counter
+  __threadfence_system();                            // every CTA's copies, before the rank counts as arrived
+  for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.gather_slot, 1u);
+  const unsigned int want = (unsigned int)p.world;
+  const unsigned long long start = global_ns();
+  bool done = false;
+  for (unsigned int i = 1; !done; ++i) {
+    unsigned int seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + p.gather_slot) : "memory");
+    done = seen >= want;
+    if (!done && (i & 63u) == 0u && (*abort_flag || global_ns() - start > kWaitLimitNs)) break;
+  }
+  if (done) atomicSub_system(mine + p.gather_slot, want);
+  else if (p.status) atomicOr(p.status, kStatusGatherTimeout);
+  __threadfence_system();
 }
 
 template <int FMT, int M, typename XT>
@@ -761,7 +779,7 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
         ok = consume_tile<FMT, M, 1, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
     }
     if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
-    if (p.world >= 1) gather_finish<CW>(p, abort_flag);
+    if (p.world >= 1) gather_finish<M, CW>(p, abort_flag);
   }
   // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
   // memory is handed to the next one (bounded sleep, error path only).

@@ -41,9 +41,9 @@ DG_API int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t
  * counterpart in the reference (it has no multi-GPU code); it is the column-sharded stack's replacement for "GEMV,
  * then NCCL all-gather". All `world` ranks (1..8, one GPU each, peers mapped into each other's address space) call
  * it in the same order with the same M, N (rows of this rank's slice), K and slot. peer_out[q] is rank q's gathered
- * buffer [world][M][N] (FP32 or x's type) and peer_flags[q] rank q's pair of zero-initialised 32-bit counters, both
+ * buffer [world][M][N] (FP32 or x's type) and peer_flags[q] rank q's block of four zero-initialised 32-bit counters, both
  * as addresses valid on the calling device (host arrays of `world` pointers, read during the call). The kernel stores
- * its [M][N] results into slot `rank` of every rank's buffer, counts itself in on every rank's counter `slot`, and
+ * its [M][N] results into slot `rank` of every rank's buffer, counts the rank in on every rank's counter `slot`, and
  * ends only when every rank's results have arrived in this rank's buffer (bounded wait: dg_take_status bit 2 on
  * time-out). Consecutive calls alternate slot 0 and 1. */
 DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
@@ -57,19 +57,19 @@ DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, con
  * nothing left for cudaMalloc afterwards; a plugin host or a latency-critical decode loop that forbids allocation
  * after initialisation because cudaMalloc synchronises the device and can fail; code that only learns it needs the
  * counters while a stream is being captured. Such callers own the gathered output buffers already, but have no
- * memory for the arrival counters the fused all-gather needs. Here the counters are DG_NOALLOC_CHANNELS pairs built
- * into the library (512 bytes on every GPU that loads it, until the process exits); this call and everything under
+ * memory for the arrival counters the fused all-gather needs. Here the counters are DG_NOALLOC_CHANNELS blocks of four built
+ * into the library (1 KB on every GPU that loads it, until the process exits); this call and everything under
  * it calls no cudaMalloc, cudaFree or other allocating routine.
  *
  * Arguments as dg_enqueue_nvfp4_allgather, except that instead of peer_flags the caller names the CUDA device
  * ordinal of every rank (devices[q], host array of `world` ints) and a channel 0 .. DG_NOALLOC_CHANNELS - 1; rank q's
- * counters are the pair `channel` in device devices[q]'s copy of the library's array, so all ranks must live in
+ * counters are block `channel` in device devices[q]'s copy of the library's array, so all ranks must live in
  * this process (one thread or stream per GPU) with peer access enabled between their devices; world = 1 needs
  * neither. More than 8 ranks or a channel outside the range is refused with cudaErrorInvalidValue (1): the built-in
  * counters cover nothing larger.
  * The first call that names a device looks up that device's array (cudaSetDevice + cudaGetSymbolAddress, then back):
  * make that first call outside any stream capture.
- * Every call on a channel shares its two counters, which keep whatever the last call left: a completed call leaves
+ * Every call on a channel shares its counters, which keep whatever the last call left: a completed call leaves
  * them zero, and that is the state the next call requires. Two calls on the same channel that overlap on the GPU, or a
  * call after one that timed out (dg_take_status bit 2), race on the counters; use another channel, or order them. */
 #define DG_NOALLOC_CHANNELS 64

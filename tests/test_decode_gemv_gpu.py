@@ -299,7 +299,7 @@ def test_one_rank_allgather_is_the_plain_gemv():
     x = wl.activations(m, k).to(dev)
     want = gemv_abi("nvfp4", x, (c, s, i), torch.bfloat16)
     full = torch.zeros(1, m, n, dtype=torch.bfloat16, device=dev)
-    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    flags = torch.zeros(4, dtype=torch.int32, device=dev)
     ptr = lambda t: ctypes.c_void_p(t.data_ptr())
     outs = (ctypes.c_void_p * 1)(full.data_ptr())
     flag_ptrs = (ctypes.c_void_p * 1)(flags.data_ptr())

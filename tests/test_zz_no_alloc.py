@@ -28,9 +28,9 @@ def test_built_in_counters_give_the_bits_of_caller_allocated_counters():
     devices = (ctypes.c_int * 1)(torch.cuda.current_device())
     for m in (1, 7, 16):
         x = wl.activations(m, k, seed=40 + m).to(dev)
-        # existing entry point: the caller allocates (and zeroes) the pair of counters
+        # existing entry point: the caller allocates (and zeroes) the block of counters
         want = torch.zeros(1, m, n, dtype=torch.bfloat16, device=dev)
-        flags = torch.zeros(2, dtype=torch.int32, device=dev)
+        flags = torch.zeros(4, dtype=torch.int32, device=dev)
         assert lib.dg_enqueue_nvfp4_allgather(_ptr(x), x.stride(0), 1, _ptr(codes), _ptr(scales), 0, _ptr(inverse),
                                               (ctypes.c_void_p * 1)(want.data_ptr()),
                                               (ctypes.c_void_p * 1)(flags.data_ptr()), 1, 0, 0, 1, m, n, k, stream) == 0
@@ -58,7 +58,7 @@ def test_sizes_beyond_the_built_in_counters_are_refused():
     devices = (ctypes.c_int * 1)(torch.cuda.current_device())
     args = lambda world, channel: (_ptr(x), x.stride(0), 1, _ptr(codes), _ptr(scales), 0, _ptr(inverse), outs, devices,
                                    world, 0, channel, 0, 1, m, n, k, None)
-    assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(1, 64)) == 1      # channel past the 64 built-in pairs
+    assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(1, 64)) == 1      # channel past the 64 built-in blocks
     assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(1, -1)) == 1
     assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(9, 0)) == 1       # more ranks than the counters cover
     assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(1, 63)) == 0      # the last channel works

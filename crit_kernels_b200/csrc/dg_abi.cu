@@ -58,6 +58,7 @@ bool encode_rows(CUtensorMap* map, const void* base, int rows, int row_bytes, in
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 DeviceState g_devices[kMaxDevices];
+std::atomic<int> g_static_weights{0};   // dg_set_static_weights
 
 const void* const* const kTables[] = {dg_table_bf16,       dg_table_fp8_bf16,   dg_table_fp8_f16,  dg_table_mxfp8_bf16,
                                       dg_table_mxfp8_f16,  dg_table_nvfp4_bf16, dg_table_nvfp4_f16};
@@ -156,9 +157,24 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   p.use_2d = p.N >= cw && encode_rows(&p.tmap_w, p.w, p.N, p.row_bytes, cw, win_bytes);
   if (p.use_2d && p.scale_mode == dg::SCALES_STAGED)
     p.use_2d = encode_rows(&p.tmap_sc, p.scales, p.N, p.scale_row_bytes, cw, p.steps * kFormats[fmt].scb);
+  p.early_weights = g_static_weights.load(std::memory_order_relaxed);
   void* args[] = {&p};
   const int threads = 32 * (dg::consumer_warps(fmt, M) + dg::producer_warps(fmt, M));
-  const cudaError_t e = cudaLaunchKernel(kTables[table][M - 1], dim3(ctas), dim3(threads), args, smem, stream);
+  // Programmatic dependent launch: the kernel may start while the previous kernel of the stream drains (its launch,
+  // barrier set-up and, with static weights, its first weight copies overlap that tail); it waits for the previous
+  // kernel before it reads activations or scales from global memory and before it writes.
+  static const bool no_pdl = std::getenv("DG_NO_PDL") != nullptr;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(ctas);
+  config.blockDim = dim3(threads);
+  config.dynamicSmemBytes = (size_t)smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = no_pdl ? 0 : 1;
+  const cudaError_t e = cudaLaunchKernelExC(&config, kTables[table][M - 1], args);
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
@@ -314,6 +330,10 @@ int dg_take_status(void) {
   return e == cudaSuccess ? word : -(int)e;
 }
 
-int dg_version(void) { return 100; }
+int dg_set_static_weights(int enabled) {
+  return g_static_weights.exchange(enabled ? 1 : 0, std::memory_order_relaxed);
+}
+
+int dg_version(void) { return 101; }
 
 }  // extern "C"

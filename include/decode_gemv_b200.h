@@ -104,6 +104,15 @@ DG_API int dg_plan(int fmt, int M, int N, int K, int plan[6]);
  * diagnostic, not part of the hot path; returns the word (0 = clean) or a negative cudaError_t. */
 DG_API int dg_take_status(void);
 
+/* Tells the library whether weights (codes, block scales staged with them, BF16 weights) are static: never written
+ * by the kernel that precedes a GEMV in its stream. Every GEMV kernel is launched with programmatic dependent launch,
+ * i.e. it may start while the previous kernel of the stream finishes; it always waits for that kernel before it reads
+ * activations, row / inverse scales or directly-read block scales and before it writes. With enabled = 1 it starts
+ * streaming weights before that wait, which hides its start-up behind the previous kernel's tail (what a decode
+ * stack with resident weights wants); with 0 (the default) nothing is read before the wait, which is correct for
+ * any caller. Process-wide; returns the previous setting. No counterpart in the reference. */
+DG_API int dg_set_static_weights(int enabled);
+
 /* Library version: 100 * major + minor. */
 DG_API int dg_version(void);
 

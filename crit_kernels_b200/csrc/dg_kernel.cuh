@@ -60,7 +60,7 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 //   class 0   M small: the kernel is HBM-bound. 12 consumer + 4 producer warps (128 registers each): as many warps
 //             as the register file gives, to hide shared-memory and conversion latencies; every SM sub-partition
 //             hosts the same number of consumers.
-//   class 1   M medium: 8 consumer + 4 producer warps (168 registers each).
+//   class 1   M medium: 10 consumer + 2 producer warps (168 registers each).
 //   class 2   M large: the kernel is FP32-FMA-bound. 6 consumer + 2 producer warps, 255 registers each.
 // Classes 0 and 1 hold the converted activations of a block and stream the rows past them; class 2 holds the rows'
 // decoded weights and streams the activation rows.
@@ -72,10 +72,10 @@ __host__ __device__ constexpr int shape_class(int fmt, int m) {
 __host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class(fmt, m) < 2; }
 // (BF16 weights, the lightest arithmetic per byte, measured 13-19 % faster with 14 + 2 warps than with 12 + 4.)
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12) : shape_class(fmt, m) == 1 ? 8 : 6;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12) : shape_class(fmt, m) == 1 ? 10 : 6;
 }
 __host__ __device__ constexpr int producer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : shape_class(fmt, m) == 1 ? 4 : 2;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : 2;
 }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }

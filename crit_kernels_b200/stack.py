@@ -167,8 +167,10 @@ class ShardedStack:
         dist.all_gather_into_tensor(full.view(-1, shard.shape[1]), shard, group=self.group)
 
     @classmethod
-    def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None, gather="fused"):
-        """`layers` x `roles` projections; every rank draws the same full matrix from the same seed and keeps its
+    def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None, gather="fused",
+               static_weights=True):
+        """`layers` x `roles` projections; static_weights: the stack's weights are resident and never rewritten, so
+        every GEMV may start streaming them while the kernel before it finishes (dg_set_static_weights); every rank draws the same full matrix from the same seed and keeps its
         rows, so the shards of all ranks together are exactly the matrix a single GPU would hold."""
         projections = []
         for layer in range(layers):
@@ -183,6 +185,9 @@ class ShardedStack:
                 del codes, scales, inverse
         if gather not in ("fused", "nccl"):
             raise ValueError(f"gather must be 'fused' or 'nccl', not {gather!r}")
+        if device.type == "cuda":
+            from . import cabi
+            cabi.load().dg_set_static_weights(1 if static_weights else 0)
         return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel(), gather)
 
     def capture(self, m):

@@ -331,7 +331,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "c1", "stack"])
     ap.add_argument("--layers", type=int, default=None, help="stack depth (default 80)")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--gather", default="fused", choices=["fused", "fused-overlap", "nccl"],
                     help="stack workload on N > 1 GPUs: all-gather fused into the GEMV epilogue, or NCCL per GEMV")
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
                     help="run `--steps` calls of one GEMV (fmt in bf16, fp8, mxfp8, nvfp4) and exit: the small case "

@@ -15,6 +15,7 @@ SIGNATURES = {
                                         _i, _i, _i, _i, _p]),
     "dg_enqueue_nvfp4_allgather_noalloc": (_i, [_p, _i, _i, _p, _p, _i, _p, ctypes.POINTER(_p), _f, _i, _i, _i, _i, _i, _i,
                                                 _i, _i, _p]),
+    "dg_enqueue_gather_wait": (_i, [_p, _i, ctypes.c_uint, _p]),
     "dg_enqueue_fp8": (_i, [_p, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_hardware_decode": (_i, []),

@@ -207,7 +207,7 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
   if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return (int)cudaErrorInvalidValue;
   if (!x || !codes || !scales || !inverse || !peer_out || !peer_flags || ldx % 8 || !aligned(x, 16) ||
       !aligned(codes, 16) || !aligned(scales, 2) || !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1) ||
-      world < 1 || world > dg::kMaxRanks || rank < 0 || rank >= world || (slot != 0 && slot != 1))
+      world < 1 || world > dg::kMaxRanks || rank < 0 || rank >= world || slot < 0 || slot > 3)
     return (int)cudaErrorInvalidValue;
   Params p{};
   p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse; p.ldo = N;
@@ -217,7 +217,7 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
   p.ct = blocked ? (K / 16 + 3) / 4 : 0;
   p.scale_mode = blocked ? dg::SCALES_BLOCKED
                          : (K % 256 == 0 && aligned(scales, 16)) ? dg::SCALES_STAGED : dg::SCALES_DIRECT;
-  p.world = world; p.rank = rank; p.gather_slot = slot;
+  p.world = world; p.rank = rank; p.gather_slot = slot & 1; p.gather_nowait = slot >> 1;
   for (int q = 0; q < world; ++q) {
     if (!peer_out[q] || !peer_flags[q] || !aligned(peer_flags[q], 4)) return (int)cudaErrorInvalidValue;
     p.peer_out[q] = peer_out[q];
@@ -225,6 +225,30 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
   }
   p.out = peer_out[rank];
   return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
+}
+
+// Waits (bounded) until counter `slot` of this rank's block holds `expected` arrivals, then takes them off.
+__global__ void gather_wait_kernel(unsigned int* counter, unsigned int expected, int* status) {
+  const unsigned long long start = dg::global_ns();
+  bool done = false;
+  for (unsigned int i = 1; !done; ++i) {
+    unsigned int seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    done = seen >= expected;
+    if (!done && (i & 63u) == 0u && dg::global_ns() - start > dg::kWaitLimitNs) break;
+  }
+  if (done) atomicSub_system(counter, expected);
+  else if (status) atomicOr(status, dg::kStatusGatherTimeout);
+  __threadfence_system();
+}
+
+int dg_enqueue_gather_wait(void* flags, int slot, unsigned int expected, void* stream) {
+  DeviceState* st = device_state();
+  if (!st) return (int)cudaErrorInvalidDevice;
+  if (!flags || !aligned(flags, 4) || (slot != 0 && slot != 1) || expected == 0) return (int)cudaErrorInvalidValue;
+  gather_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned int*>(flags) + slot, expected,
+                                                                    st->status);
+  return (int)cudaGetLastError();
 }
 
 // ---- the entry point that allocates nothing ---------------------------------------------------------------------

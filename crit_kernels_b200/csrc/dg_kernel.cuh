@@ -105,7 +105,7 @@ struct Params {
   // peer-mapped addresses) and counts itself done in word 2 of this rank's counter block; the last CTA adds 1 to
   // word `gather_slot` (0 or 1) of every rank's block (peer_flag[q]) and waits until its own word holds `world`, then
   // clears it: when the kernel ends, every rank's data has landed here.
-  int world, rank, gather_slot;
+  int world, rank, gather_slot, gather_nowait;   // nowait: signal only; dg_enqueue_gather_wait collects later
   void* peer_out[kMaxRanks];
   unsigned int* peer_flag[kMaxRanks];
   // Tensor maps over the weight rows and the row-major scale rows as 8-byte elements: box = (consumer warps) rows
@@ -771,6 +771,7 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
   atomicExch(mine + 2, 0u);                          // last CTA of the rank: re-arm the CTA counter
   __threadfence_system();                            // every CTA's copies, before the rank counts as arrived
   for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.gather_slot, 1u);
+  if (p.gather_nowait) return;
   const unsigned int want = (unsigned int)p.world;
   const unsigned long long start = global_ns();
   bool done = false;

@@ -76,8 +76,9 @@ class StackRun:
         self.x = {role: t.to(dev) for role, t in self.x_host.items()}
         self.shard = {role: torch.empty(m, n // stack.world, dtype=torch.bfloat16, device=dev)
                       for role, _, n in stack.roles}
-        self.fused = FusedGatherBuffers(stack, m) if stack.world > 1 and stack.gather == "fused" else None
+        self.fused = FusedGatherBuffers(stack, m) if stack.world > 1 and stack.gather.startswith("fused") else None
         self.calls = 0
+        self.pending = [0, 0]
         self.full = self.fused.full if self.fused else {
             role: torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16, device=dev)
             for role, _, n in stack.roles}
@@ -93,28 +94,48 @@ class StackRun:
         st = self.stack
         for p in st.projections:
             if self.fused:
-                self._gemv_allgather(p)
+                self._gemv_allgather(p, overlap=st.gather == "fused-overlap")
             else:
                 st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
                 if st.world > 1:
                     st.nccl_gather(self.full[p.role], self.shard[p.role])
             if st.world > 1:
                 if keep is not None:
+                    if self.fused and st.gather == "fused-overlap":
+                        self._collect()              # a test reads this projection's output now
                     keep.append(self.full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone())
             elif keep is not None:
                 keep.append(self.shard[p.role].clone())
+        if self.fused and st.gather == "fused-overlap":
+            self._collect()
 
-    def _gemv_allgather(self, p):
+    def _collect(self):
+        """End of an overlapped pass: wait for every rank's arrivals of the GEMVs enqueued since the last collect."""
+        from . import cabi
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        base = ctypes.c_void_p(self.fused.arena.data_ptr())
+        for slot in (0, 1):
+            calls = self.pending[slot]
+            if calls:
+                code = cabi.load().dg_enqueue_gather_wait(base, slot, calls * self.stack.world, stream)
+                if code:
+                    raise RuntimeError(f"dg_enqueue_gather_wait: cudaError {code}")
+                self.pending[slot] = 0
+
+    def _gemv_allgather(self, p, overlap=False):
         """The GEMV with the all-gather in its epilogue (C ABI dg_enqueue_nvfp4_allgather) on the current stream."""
         from . import cabi
         st, x = self.stack, self.x[p.role]
         ptr = lambda t: ctypes.c_void_p(t.data_ptr())
         code = cabi.load().dg_enqueue_nvfp4_allgather(
             ptr(x), x.stride(0), 1, ptr(p.codes), ptr(p.scales), 0, ptr(p.inverse), self.fused.out_ptrs[p.role],
-            self.fused.flag_ptrs, st.world, st.rank, self.calls & 1, 1, self.m, p.codes.shape[0], p.k,
+            self.fused.flag_ptrs, st.world, st.rank, (self.calls & 1) + (2 if overlap else 0), 1, self.m,
+            p.codes.shape[0], p.k,
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
         if code:
             raise RuntimeError(f"dg_enqueue_nvfp4_allgather: cudaError {code}")
+        if overlap:
+            self.pending[self.calls & 1] += 1
         self.calls += 1
 
     def capture(self):
@@ -160,6 +181,9 @@ class ShardedStack:
             return "none (1 GPU)"
         if self.gather == "fused":
             return "fused into the GEMV epilogue: peer stores into every rank's symmetric buffer + arrival counters"
+        if self.gather == "fused-overlap":
+            return ("fused into the GEMV epilogue, arrivals collected once at the end of the pass (legal only because "
+                    "the stack's GEMVs do not consume each other's outputs)")
         return "NCCL all_gather_into_tensor after every GEMV, inside the graph"
 
     def nccl_gather(self, full, shard):
@@ -183,8 +207,8 @@ class ShardedStack:
                 projections.append(Projection(role, k, n, codes[lo:hi].clone(), scales[lo:hi].clone(),
                                               inverse[lo:hi].clone()))
                 del codes, scales, inverse
-        if gather not in ("fused", "nccl"):
-            raise ValueError(f"gather must be 'fused' or 'nccl', not {gather!r}")
+        if gather not in ("fused", "fused-overlap", "nccl"):
+            raise ValueError(f"gather must be 'fused', 'fused-overlap' or 'nccl', not {gather!r}")
         if device.type == "cuda":
             from . import cabi
             cabi.load().dg_set_static_weights(1 if static_weights else 0)

@@ -45,11 +45,19 @@ DG_API int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t
  * as addresses valid on the calling device (host arrays of `world` pointers, read during the call). The kernel stores
  * its [M][N] results into slot `rank` of every rank's buffer, counts the rank in on every rank's counter `slot`, and
  * ends only when every rank's results have arrived in this rank's buffer (bounded wait: dg_take_status bit 2 on
- * time-out). Consecutive calls alternate slot 0 and 1. */
+ * time-out). Consecutive calls alternate slot 0 and 1. With slot 2 or 3 the kernel uses counter slot - 2 and does
+ * not wait: it only delivers its results and counts the rank in, so that GEMVs whose inputs do not depend on the
+ * gathered outputs overlap their gathers; dg_enqueue_gather_wait then collects the arrivals. */
 DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
                                       int blocked, const float* inverse, void* const* peer_out,
                                       void* const* peer_flags, int world, int rank, int slot, int out_kind, int M,
                                       int N, int K, void* stream);
+
+/* Collects the arrivals of all-gather calls made with slot 2 or 3: enqueues a one-thread kernel that waits (bounded,
+ * dg_take_status bit 2 on time-out) until counter `slot` (0 or 1) of this rank's block `flags` holds `expected` =
+ * (calls made on that counter) x world arrivals and takes them off. When it has run, the results of all those calls
+ * from every rank are in this rank's buffers. No counterpart in the reference. */
+DG_API int dg_enqueue_gather_wait(void* flags, int slot, unsigned int expected, void* stream);
 
 /* dg_enqueue_nvfp4_allgather for callers that cannot allocate device memory. No counterpart in the reference.
  *

@@ -48,13 +48,13 @@ def _worker(rank, world, port, gather, results):
         guard.cancel()
 
 
-@pytest.mark.parametrize("gather", ["fused", "nccl"])
+@pytest.mark.parametrize("gather", ["fused", "fused-overlap", "nccl"])
 @pytest.mark.parametrize("world", [2, 4])
 def test_sharded_stack_reproduces_the_single_gpu_bits(world, gather):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as manager:
         results = manager.dict()
-        mp.spawn(_worker, args=(world, 29531 + world + (10 if gather == "fused" else 0), gather, results), nprocs=world,
+        mp.spawn(_worker, args=(world, 29531 + world + {"fused": 10, "fused-overlap": 20, "nccl": 0}[gather], gather, results), nprocs=world,
                  join=True)
         assert dict(results) == {r: "ok" for r in range(world)}

@@ -765,12 +765,16 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
   }
   asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
   if (tid != 0) return;
+  // System-scope operations cost about a microsecond each and this is the kernel's tail, so the chain is kept short:
+  // fence (the CTA's peer copies), one acquire-release count per CTA, then the last CTA releases one arrival per rank.
   unsigned int* mine = p.peer_flag[p.rank];
-  __threadfence_system();                            // the CTA's copies, before it counts as done
-  if (atomicAdd(mine + 2, 1u) != gridDim.x - 1) return;
-  atomicExch(mine + 2, 0u);                          // last CTA of the rank: re-arm the CTA counter
-  __threadfence_system();                            // every CTA's copies, before the rank counts as arrived
-  for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.gather_slot, 1u);
+  if (p.world > 1) __threadfence_system();           // the CTA's copies, before it counts as done
+  unsigned int before;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(mine + 2) : "memory");
+  if (before != gridDim.x - 1) return;
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(mine + 2), "r"(0u) : "memory");   // re-arm the CTA count
+  for (int q = 0; q < p.world; ++q)                  // release: every CTA's copies precede the rank's arrival
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[q] + p.gather_slot) : "memory");
   if (p.gather_nowait) return;
   const unsigned int want = (unsigned int)p.world;
   const unsigned long long start = global_ns();
@@ -781,9 +785,10 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
     done = seen >= want;
     if (!done && (i & 63u) == 0u && (*abort_flag || global_ns() - start > kWaitLimitNs)) break;
   }
-  if (done) atomicSub_system(mine + p.gather_slot, want);
-  else if (p.status) atomicOr(p.status, kStatusGatherTimeout);
-  __threadfence_system();
+  if (done)
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mine + p.gather_slot), "r"(0u - want) : "memory");
+  else if (p.status)
+    atomicOr(p.status, kStatusGatherTimeout);
 }
 
 template <int FMT, int M, typename XT>

@@ -119,6 +119,54 @@ struct Params {
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Shared-memory loads by 32-bit shared-space address: the ring is addressed with one base register per stage plus
+// constants, instead of 64-bit generic pointer arithmetic per load. Volatile keeps them after the barrier waits.
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// Two FP32 values in one 64-bit register pair, the operand form of the packed fma.rn.f32x2 / mul.rn.f32x2. Operands
+// are packed once where they are produced and accumulators stay packed across the whole K loop, so that no
+// pack / unpack moves surround the FMAs (measured: almost one extra instruction per packed FMA otherwise).
+struct pk2 { unsigned long long v; };
+__device__ __forceinline__ pk2 pack2(float lo, float hi) {
+  pk2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ pk2 pack2_bits(uint32_t lo, uint32_t hi) {
+  pk2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ float sum2(pk2 a) {   // low + high
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v));
+  return lo + hi;
+}
+__device__ __forceinline__ pk2 ffma2(pk2 a, pk2 b, pk2 c) {   // (a.lo * b.lo + c.lo, a.hi * b.hi + c.hi), each IEEE RN
+  pk2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d.v) : "l"(a.v), "l"(b.v), "l"(c.v));
+  return d;
+}
+__device__ __forceinline__ pk2 fmul2(pk2 a, pk2 b) {
+  pk2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
+  return d;
+}
+
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -182,19 +230,19 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 // ---------------------------------------------------------------------------------------------------------------
 // Element conversions. All exact.
 
-__device__ __forceinline__ float2 pair_to_f32(uint32_t v, __nv_bfloat16) {   // two BF16 -> two FP32
-  // byte permute for the low element: keeps the shift off the FMA pipe, which the packed FMAs need
-  return make_float2(__uint_as_float(__byte_perm(v, 0u, 0x1044u)), __uint_as_float(v & 0xffff0000u));
+__device__ __forceinline__ pk2 half2_bits_to_f32(uint32_t h) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+  return pack2(f.x, f.y);
 }
-__device__ __forceinline__ float2 pair_to_f32(uint32_t v, __half) {          // two FP16 -> two FP32
-  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+__device__ __forceinline__ pk2 pair_to_f32(uint32_t v, __nv_bfloat16) {   // two BF16 -> two FP32
+  // byte permute for the low element: keeps the shift off the FMA pipe, which the packed FMAs need
+  return pack2_bits(__byte_perm(v, 0u, 0x1044u), v & 0xffff0000u);
+}
+__device__ __forceinline__ pk2 pair_to_f32(uint32_t v, __half) {          // two FP16 -> two FP32
+  return half2_bits_to_f32(v);
 }
 __device__ __forceinline__ float2 e4m3x2_to_f32(uint32_t v) {                // low 16 bits: two E4M3 -> two FP32
   const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
-  return __half22float2(*reinterpret_cast<const __half2*>(&h));
-}
-__device__ __forceinline__ float2 e2m1x2_to_f32(uint32_t v) {                // low 8 bits: two E2M1 -> two FP32
-  const __half2_raw h = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)v, __NV_E2M1);
   return __half22float2(*reinterpret_cast<const __half2*>(&h));
 }
 // E8M0 exponent byte as FP32 2^(e-127); e = 0 is the FP32 subnormal 2^-127 and e = 255 is NaN, as the reference
@@ -236,17 +284,16 @@ struct Walk {
 __host__ __device__ constexpr int scale_group_bytes(int cw, int steps, int scb) { return (cw * steps * scb + 127) & ~127; }
 
 // Shared-memory stage: [weights rows_cap x win_bytes][scales: r groups of CW rows x steps*SCB, each group padded to
-// 128 bytes][x M x steps*64*E bytes]. Tile row t = w + CW * g is row w of group g.
+// 128 bytes][x: steps x M x 64*E bytes, the activations of one 512-byte step of every activation row together]. Tile row t = w + CW * g is row w of group g.
 template <int FMT, int M, int CW>
 struct StageLayout {
   static constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB;
-  int w_row, sc_row, sc_group, x_row, sc_off, x_off;
+  int w_row, sc_row, sc_group, sc_off, x_off;
   __device__ __forceinline__ StageLayout(const Params& p) {
     const int rows_cap = CW * p.rows_per_warp;
     w_row = p.steps * kStepBytes;
     sc_row = p.steps * SCB;
     sc_group = scale_group_bytes(CW, p.steps, SCB);
-    x_row = p.steps * 64 * E;
     sc_off = rows_cap * w_row;
     x_off = sc_off + p.rows_per_warp * sc_group;
   }
@@ -324,11 +371,15 @@ struct Producer {
     const int slots = (wbytes >> 4) * NQ;
     const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
     const unsigned char* xg = reinterpret_cast<const unsigned char*>(p.x);
+    constexpr int STEP_SLOTS = 32 * NQ;              // 16-byte slots of one step of one activation row (64 * E bytes)
 #pragma unroll 1
     for (int m = 0; m < M; ++m) {
-      const uint32_t dst = stage + lay.x_off + m * lay.x_row;
+      const uint32_t dst = stage + lay.x_off + m * (64 * E);
       const unsigned char* src = xg + (size_t)m * p.ldx * 2 + xbyte0;
-      for (int sl = pl; sl < slots; sl += PL) cp_async16(dst + swizzle_slot<NQ>(sl) * 16, src + (size_t)sl * 16);
+      for (int sl = pl; sl < slots; sl += PL) {
+        const int st = sl / STEP_SLOTS, in_step = sl - st * STEP_SLOTS;
+        cp_async16(dst + st * (M * 64 * E) + swizzle_slot<NQ>(in_step) * 16, src + (size_t)sl * 16);
+      }
     }
     cp_async_arrive_noinc(full);
   }
@@ -379,33 +430,30 @@ struct XOffsets {   // byte offsets of the lane's NQ swizzled slots inside one s
 };
 
 template <typename XT>
-__device__ __forceinline__ void load_x8(const unsigned char* p, float2 (&x)[4]) {   // 8 activations -> 4 FP32 pairs
-  const uint4 v = *reinterpret_cast<const uint4*>(p);
+__device__ __forceinline__ void load_x8(uint32_t addr, pk2 (&x)[4]) {   // 8 activations -> 4 FP32 pairs
+  const uint4 v = lds128(addr);
   x[0] = pair_to_f32(v.x, XT());
   x[1] = pair_to_f32(v.y, XT());
   x[2] = pair_to_f32(v.z, XT());
   x[3] = pair_to_f32(v.w, XT());
 }
-__device__ __forceinline__ float2 fma4(const float2 (&w)[4], const float2 (&x)[4], float2 a) {
-  a = __ffma2_rn(w[0], x[0], a);
-  a = __ffma2_rn(w[1], x[1], a);
-  a = __ffma2_rn(w[2], x[2], a);
-  return __ffma2_rn(w[3], x[3], a);
+__device__ __forceinline__ pk2 fma4(const pk2 (&w)[4], const pk2 (&x)[4], pk2 a) {
+  a = ffma2(w[0], x[0], a);
+  a = ffma2(w[1], x[1], a);
+  a = ffma2(w[2], x[2], a);
+  return ffma2(w[3], x[3], a);
 }
 
 // 8 weights of a sub-block as 4 FP32 pairs.
-__device__ __forceinline__ void decode_bf16(const uint4& v, float2 (&w)[4]) {
+__device__ __forceinline__ void decode_bf16(const uint4& v, pk2 (&w)[4]) {
   w[0] = pair_to_f32(v.x, __nv_bfloat16());
   w[1] = pair_to_f32(v.y, __nv_bfloat16());
   w[2] = pair_to_f32(v.z, __nv_bfloat16());
   w[3] = pair_to_f32(v.w, __nv_bfloat16());
 }
-__device__ __forceinline__ float2 half2_bits_to_f32(uint32_t h) {
-  return __half22float2(*reinterpret_cast<const __half2*>(&h));
-}
 // The conversions take their packed source from a 16-bit (E4M3 pair) or 8-bit (E2M1 pair) register; unpacking the
 // word in PTX lets the assembler select the sub-word instead of shifting it out first.
-__device__ __forceinline__ void decode_e4m3(uint32_t a, uint32_t b, float2 (&w)[4]) {
+__device__ __forceinline__ void decode_e4m3(uint32_t a, uint32_t b, pk2 (&w)[4]) {
   uint32_t h0, h1, h2, h3;
   asm("{\n\t.reg .b16 lo, hi;\n\t"
       "mov.b32 {lo, hi}, %2;\n\t"
@@ -422,7 +470,7 @@ __device__ __forceinline__ void decode_e4m3(uint32_t a, uint32_t b, float2 (&w)[
   w[2] = half2_bits_to_f32(h2);
   w[3] = half2_bits_to_f32(h3);
 }
-__device__ __forceinline__ void decode_e2m1(uint32_t a, float2 (&w)[4]) {
+__device__ __forceinline__ void decode_e2m1(uint32_t a, pk2 (&w)[4]) {
   uint32_t h0, h1, h2, h3;
   asm("{\n\t.reg .b8 c0, c1, c2, c3;\n\t"
       "mov.b32 {c0, c1, c2, c3}, %4;\n\t"
@@ -438,30 +486,30 @@ __device__ __forceinline__ void decode_e2m1(uint32_t a, float2 (&w)[4]) {
 }
 
 template <bool FEW, int M, int R, typename XT>
-__device__ __forceinline__ void body_bf16(const unsigned char* wrow, const int (&woff)[R], const unsigned char* xs,
-                                          int x_row, float2 (&acc)[R][M]) {
+__device__ __forceinline__ void body_bf16(uint32_t wrow, const uint32_t (&woff)[R], uint32_t xs, pk2 (&acc)[R][M]) {
+  constexpr int XROW = 64 * Format<FMT_BF16>::E;   // bytes between activation rows inside a step
   uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + woff[r]);
+  for (int r = 0; r < R; ++r) wv[r] = lds128(wrow + woff[r]);
   if constexpr (FEW) {
-    float2 xf[M][4];
+    pk2 xf[M][4];
 #pragma unroll
-    for (int m = 0; m < M; ++m) load_x8<XT>(xs + m * x_row, xf[m]);
+    for (int m = 0; m < M; ++m) load_x8<XT>(xs + m * XROW, xf[m]);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      float2 wf[4];
+      pk2 wf[4];
       decode_bf16(wv[r], wf);
 #pragma unroll
       for (int m = 0; m < M; ++m) acc[r][m] = fma4(wf, xf[m], acc[r][m]);
     }
   } else {
-    float2 wf[R][4];
+    pk2 wf[R][4];
 #pragma unroll
     for (int r = 0; r < R; ++r) decode_bf16(wv[r], wf[r]);
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-      float2 xf[4];
-      load_x8<XT>(xs + m * x_row, xf);
+      pk2 xf[4];
+      load_x8<XT>(xs + m * XROW, xf);
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r][m] = fma4(wf[r], xf, acc[r][m]);
     }
@@ -471,45 +519,45 @@ __device__ __forceinline__ void body_bf16(const unsigned char* wrow, const int (
 // FP8 / MXFP8: the block is two sub-blocks of 8 weights (words 0-1, words 2-3). `sc` holds the MXFP8 scale of each
 // row's block (unused for FP8): every weight is multiplied by it (exact: a power of two).
 template <bool FEW, bool MX, int M, int R, typename XT>
-__device__ __forceinline__ void body_fp8(const unsigned char* wrow, const int (&woff)[R], const float (&sc)[R],
-                                         const unsigned char* xs, int x_row, const XOffsets<2>& xo,
-                                         float2 (&acc)[R][M]) {
+__device__ __forceinline__ void body_fp8(uint32_t wrow, const uint32_t (&woff)[R], const float (&sc)[R], uint32_t xs,
+                                         const XOffsets<2>& xo, pk2 (&acc)[R][M]) {
+  constexpr int XROW = 64 * Format<FMT_FP8>::E;   // bytes between activation rows inside a step
   uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + woff[r]);
+  for (int r = 0; r < R; ++r) wv[r] = lds128(wrow + woff[r]);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     if constexpr (FEW) {
-      float2 xf[M][4];
+      pk2 xf[M][4];
 #pragma unroll
-      for (int m = 0; m < M; ++m) load_x8<XT>(xs + m * x_row + xo.off[j], xf[m]);
+      for (int m = 0; m < M; ++m) load_x8<XT>(xs + m * XROW + xo.off[j], xf[m]);
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        float2 wf[4];
+        pk2 wf[4];
         decode_e4m3(j ? wv[r].z : wv[r].x, j ? wv[r].w : wv[r].y, wf);
         if (MX) {
-          const float2 s2 = make_float2(sc[r], sc[r]);
+          const pk2 s2 = pack2(sc[r], sc[r]);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) wf[q] = __fmul2_rn(wf[q], s2);
+          for (int q = 0; q < 4; ++q) wf[q] = fmul2(wf[q], s2);
         }
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[r][m] = fma4(wf, xf[m], acc[r][m]);
       }
     } else {
-      float2 wf[R][4];
+      pk2 wf[R][4];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         decode_e4m3(j ? wv[r].z : wv[r].x, j ? wv[r].w : wv[r].y, wf[r]);
         if (MX) {
-          const float2 s2 = make_float2(sc[r], sc[r]);
+          const pk2 s2 = pack2(sc[r], sc[r]);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) wf[r][q] = __fmul2_rn(wf[r][q], s2);
+          for (int q = 0; q < 4; ++q) wf[r][q] = fmul2(wf[r][q], s2);
         }
       }
 #pragma unroll
       for (int m = 0; m < M; ++m) {
-        float2 xf[4];
-        load_x8<XT>(xs + m * x_row + xo.off[j], xf);
+        pk2 xf[4];
+        load_x8<XT>(xs + m * XROW + xo.off[j], xf);
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r][m] = fma4(wf[r], xf, acc[r][m]);
       }
@@ -520,43 +568,43 @@ __device__ __forceinline__ void body_fp8(const unsigned char* wrow, const int (&
 // NVFP4: the block is 32 codes = two scale blocks of 16 (words 0-1 with scale .x, words 2-3 with scale .y). The 16
 // products of a scale block are summed first (two chains of 8, started by a multiply), then acc = fma(scale,
 // partial, acc).
-__device__ __forceinline__ float2 dot16(const float2 (&wa)[4], const float2 (&wb)[4], const float2 (&xa)[4],
-                                        const float2 (&xb)[4]) {
-  float2 part = __fmul2_rn(wa[0], xa[0]);
-  part = __ffma2_rn(wa[1], xa[1], part);
-  part = __ffma2_rn(wa[2], xa[2], part);
-  part = __ffma2_rn(wa[3], xa[3], part);
+__device__ __forceinline__ pk2 dot16(const pk2 (&wa)[4], const pk2 (&wb)[4], const pk2 (&xa)[4],
+                                     const pk2 (&xb)[4]) {
+  pk2 part = fmul2(wa[0], xa[0]);
+  part = ffma2(wa[1], xa[1], part);
+  part = ffma2(wa[2], xa[2], part);
+  part = ffma2(wa[3], xa[3], part);
   return fma4(wb, xb, part);
 }
 
 template <bool FEW, int M, int R, typename XT>
-__device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, const int (&woff)[R], const float2 (&sc)[R],
-                                           const unsigned char* xs, int x_row, const XOffsets<4>& xo,
-                                           float2 (&acc)[R][M]) {
+__device__ __forceinline__ void body_nvfp4(uint32_t wrow, const uint32_t (&woff)[R], const float2 (&sc)[R], uint32_t xs,
+                                           const XOffsets<4>& xo, pk2 (&acc)[R][M]) {
+  constexpr int XROW = 64 * Format<FMT_NVFP4>::E;   // bytes between activation rows inside a step
   uint4 wv[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) wv[r] = *reinterpret_cast<const uint4*>(wrow + woff[r]);
+  for (int r = 0; r < R; ++r) wv[r] = lds128(wrow + woff[r]);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if constexpr (FEW) {
-      float2 xa[M][4], xb[M][4];
+      pk2 xa[M][4], xb[M][4];
 #pragma unroll
       for (int m = 0; m < M; ++m) {
-        load_x8<XT>(xs + m * x_row + xo.off[2 * h], xa[m]);
-        load_x8<XT>(xs + m * x_row + xo.off[2 * h + 1], xb[m]);
+        load_x8<XT>(xs + m * XROW + xo.off[2 * h], xa[m]);
+        load_x8<XT>(xs + m * XROW + xo.off[2 * h + 1], xb[m]);
       }
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        float2 wa[4], wb[4];
+        pk2 wa[4], wb[4];
         decode_e2m1(h ? wv[r].z : wv[r].x, wa);
         decode_e2m1(h ? wv[r].w : wv[r].y, wb);
         const float s = h ? sc[r].y : sc[r].x;
 #pragma unroll
         for (int m = 0; m < M; ++m)
-          acc[r][m] = __ffma2_rn(make_float2(s, s), dot16(wa, wb, xa[m], xb[m]), acc[r][m]);
+          acc[r][m] = ffma2(pack2(s, s), dot16(wa, wb, xa[m], xb[m]), acc[r][m]);
       }
     } else {
-      float2 wa[R][4], wb[R][4];
+      pk2 wa[R][4], wb[R][4];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         decode_e2m1(h ? wv[r].z : wv[r].x, wa[r]);
@@ -564,13 +612,13 @@ __device__ __forceinline__ void body_nvfp4(const unsigned char* wrow, const int 
       }
 #pragma unroll
       for (int m = 0; m < M; ++m) {
-        float2 xa[4], xb[4];
-        load_x8<XT>(xs + m * x_row + xo.off[2 * h], xa);
-        load_x8<XT>(xs + m * x_row + xo.off[2 * h + 1], xb);
+        pk2 xa[4], xb[4];
+        load_x8<XT>(xs + m * XROW + xo.off[2 * h], xa);
+        load_x8<XT>(xs + m * XROW + xo.off[2 * h + 1], xb);
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const float s = h ? sc[r].y : sc[r].x;
-          acc[r][m] = __ffma2_rn(make_float2(s, s), dot16(wa[r], wb[r], xa, xb), acc[r][m]);
+          acc[r][m] = ffma2(pack2(s, s), dot16(wa[r], wb[r], xa, xb), acc[r][m]);
         }
       }
     }
@@ -642,43 +690,44 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
   constexpr bool FEW = few_rows(FMT, M);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const XOffsets<NQ> xo(lane);
-  float2 acc[R][M];
+  pk2 acc[R][M];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = make_float2(0.f, 0.f);
+    for (int m = 0; m < M; ++m) acc[r][m] = pack2(0.f, 0.f);
   // Offsets of the warp's rows inside a stage (rows are CW tile rows and one scale group apart); rows the warp does
   // not have alias its last real row (their sums are discarded).
-  int woff[R], scoff[R];
+  uint32_t woff[R], scoff[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int rr = min(r, max(nr, 1) - 1);
-    woff[r] = (warp + CW * rr) * lay.w_row + lane * 16;
-    scoff[r] = lay.sc_off + warp * lay.sc_row + rr * lay.sc_group;
+    woff[r] = (uint32_t)((warp + CW * rr) * lay.w_row + lane * 16);
+    scoff[r] = (uint32_t)(lay.sc_off + warp * lay.sc_row + rr * lay.sc_group + (SCB == 64 ? lane * 2 : lane >> 1));
   }
   const bool staged = SCB != 0 && p.scale_mode == SCALES_STAGED;
+  const uint32_t ring = smem_addr(smem) + kSmemHeader;
 
   for (int win = 0; win < wk.nwin; ++win) {
     if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;
     if (nr > 0) {
-      const unsigned char* stage = smem + kSmemHeader + (size_t)s * p.stage_bytes;
+      const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
       const int blk0 = win * p.steps * 32;
       const int nsteps = min(p.steps, (p.nblk - blk0 + 31) >> 5);
       for (int st = 0; st < nsteps; ++st) {
         const int blk = blk0 + st * 32 + lane;
         if (blk < p.nblk) {
-          const unsigned char* wrow = stage + st * kStepBytes;
-          const unsigned char* xs = stage + lay.x_off + st * (64 * E);
+          const uint32_t wrow = stage + st * kStepBytes;
+          const uint32_t xs = stage + lay.x_off + st * (M * 64 * E);
           if constexpr (FMT == FMT_BF16) {
-            body_bf16<FEW, M, R, XT>(wrow, woff, xs + lane * 16, lay.x_row, acc);
+            body_bf16<FEW, M, R, XT>(wrow, woff, xs + lane * 16, acc);
           } else if constexpr (FMT == FMT_FP8) {
             float none[R];
-            body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, lay.x_row, xo, acc);
+            body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, xo, acc);
           } else if constexpr (FMT == FMT_MXFP8) {
             float sc[R];
             if (staged) {
 #pragma unroll
-              for (int r = 0; r < R; ++r) sc[r] = e8m0_to_f32(stage[scoff[r] + st * SCB + (lane >> 1)]);
+              for (int r = 0; r < R; ++r) sc[r] = e8m0_to_f32(lds_u8(stage + scoff[r] + st * SCB));
             } else {
 #pragma unroll
               for (int r = 0; r < R; ++r) {
@@ -686,13 +735,12 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
                 sc[r] = e8m0_to_f32(__ldg(p.scales + (size_t)n * p.scale_row_bytes + (blk >> 1)));
               }
             }
-            body_fp8<FEW, true, M, R, XT>(wrow, woff, sc, xs, lay.x_row, xo, acc);
+            body_fp8<FEW, true, M, R, XT>(wrow, woff, sc, xs, xo, acc);
           } else {
             float2 sc[R];
             if (staged) {
 #pragma unroll
-              for (int r = 0; r < R; ++r)
-                sc[r] = e4m3x2_to_f32(*reinterpret_cast<const uint16_t*>(stage + scoff[r] + st * SCB + lane * 2));
+              for (int r = 0; r < R; ++r) sc[r] = e4m3x2_to_f32(lds_u16(stage + scoff[r] + st * SCB));
             } else {
 #pragma unroll
               for (int r = 0; r < R; ++r) {
@@ -702,7 +750,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
                 sc[r] = e4m3x2_to_f32(__ldg(reinterpret_cast<const uint16_t*>(p.scales + off)));
               }
             }
-            body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, lay.x_row, xo, acc);
+            body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, xo, acc);
           }
         }
       }
@@ -718,7 +766,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int m = 0; m < M; ++m) val[r * M + m] = acc[r][m].x + acc[r][m].y;
+    for (int m = 0; m < M; ++m) val[r * M + m] = sum2(acc[r][m]);
   float total[(V + 31) / 32];
   LaneReduce<V, 16, (V + 31) / 32>::run(val, lane, total);
 #pragma unroll

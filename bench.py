@@ -36,6 +36,9 @@ import torch  # noqa: E402
 
 C1 = {"fmt": "fp8", "N": 28672, "K": 8192, "Ms": (1, 2, 4, 8, 16)}
 STACK_MS = (1, 8, 16)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the c1 kernels, from the ncu captures summarised in
+# profiles/gemv_fp8_m1_28672x8192.md and profiles/gemv_fp8_m16_28672x8192.md (algorithmic bytes: 234,995,712).
+NCU_TRAFFIC_C1 = {1: 240_238_592, 16: 243_822_336}
 METRIC = "decode_gemv_weight_stream"
 UNIT = "TB/s"
 
@@ -369,7 +372,7 @@ def main():
         top = max(range(len(ms)), key=lambda i: r["per_m_ms"][i])
         roofline = {"bound": "hbm", "kernel": f"gemv_kernel<FP8, M={ms[top]}, bf16>",
                     "achieved": detail[top]["GBps"], "peak": hbm_gbs, "unit": "GB/s",
-                    "frac": detail[top]["frac_hbm"], "traffic": None, "peak_kind": peak_kind,
+                    "frac": detail[top]["frac_hbm"], "traffic": NCU_TRAFFIC_C1.get(ms[top]), "peak_kind": peak_kind,
                     "frac_fp32_fma_ceiling": detail[top]["frac_fp32_fma"], "per_m": detail}
         config = {"workload": "c1: FP8 E4M3 W8A16 GEMV K=8192 N=28672, one call at each M in {1,2,4,8,16} per step",
                   "l2": "each call streams its own 235 MB copy of the weights (5 copies in rotation, 126 MB L2)",

@@ -800,15 +800,20 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
   const int lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
   const int rows = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x) - lo;
   const size_t slot0 = (size_t)p.rank * M * p.ldo + lo;
-  for (int q = 0; q < p.world; ++q) {
-    if (q == p.rank) continue;
-    for (int i = tid; i < M * rows; i += CW * 32) {
-      const int m = i / rows, r = i - m * rows;
-      const size_t idx = slot0 + (size_t)m * p.ldo + r;
-      if (p.out_kind == OUT_F32)
-        reinterpret_cast<float*>(p.peer_out[q])[idx] = reinterpret_cast<const float*>(p.out)[idx];
-      else
-        reinterpret_cast<uint16_t*>(p.peer_out[q])[idx] = reinterpret_cast<const uint16_t*>(p.out)[idx];
+  // warp w copies activation rows w, w + CW, ...; its lanes run along the CTA's rows (consecutive addresses)
+  const int lane = tid & 31, warp = tid >> 5;
+  for (int m = warp; m < M; m += CW) {
+    const size_t idx0 = slot0 + (size_t)m * p.ldo;
+    for (int r = lane; r < rows; r += 32) {
+      if (p.out_kind == OUT_F32) {
+        const float v = reinterpret_cast<const float*>(p.out)[idx0 + r];
+        for (int q = 0; q < p.world; ++q)
+          if (q != p.rank) reinterpret_cast<float*>(p.peer_out[q])[idx0 + r] = v;
+      } else {
+        const uint16_t v = reinterpret_cast<const uint16_t*>(p.out)[idx0 + r];
+        for (int q = 0; q < p.world; ++q)
+          if (q != p.rank) reinterpret_cast<uint16_t*>(p.peer_out[q])[idx0 + r] = v;
+      }
     }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");

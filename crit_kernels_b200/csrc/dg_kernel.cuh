@@ -819,15 +819,20 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
   asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
   if (tid != 0) return;
   // System-scope operations cost about a microsecond each and this is the kernel's tail, so the chain is kept short:
-  // fence (the CTA's peer copies), one acquire-release count per CTA, then the last CTA releases one arrival per rank.
+  // fence (the CTA's peer copies), one acquire-release count per CTA, then the last CTA fences once and sends one
+  // relaxed arrival per rank.
   unsigned int* mine = p.peer_flag[p.rank];
   if (p.world > 1) __threadfence_system();           // the CTA's copies, before it counts as done
   unsigned int before;
   asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(before) : "l"(mine + 2) : "memory");
   if (before != gridDim.x - 1) return;
   asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(mine + 2), "r"(0u) : "memory");   // re-arm the CTA count
-  for (int q = 0; q < p.world; ++q)                  // release: every CTA's copies precede the rank's arrival
-    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[q] + p.gather_slot) : "memory");
+  // One system-scope fence orders every CTA's copies (observed through the count) before the arrivals; the
+  // arrivals themselves are relaxed, so that they leave back to back (a release per arrival serialised eight
+  // round trips on eight GPUs).
+  __threadfence_system();
+  for (int q = 0; q < p.world; ++q)
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[q] + p.gather_slot) : "memory");
   if (p.gather_nowait) return;
   const unsigned int want = (unsigned int)p.world;
   const unsigned long long start = global_ns();

@@ -16,7 +16,10 @@ LIB = os.path.join(OUT_DIR, "libdecode_gemv_ref.so")
 NVCC = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
 
 
-def build(reference="/root/reference", verbose=True):
+REFERENCE = os.environ.get("CRIT_KERNELS_REFERENCE", "/root/reference")   # the reference checkout
+
+
+def build(reference=REFERENCE, verbose=True):
     src_dir = os.path.join(reference, "decode-gemv", "decode_gemv_cuda")
     src = os.path.join(src_dir, "decode_gemv.cu")
     shim = os.path.join(HERE, "ref_shim.cu")
@@ -49,5 +52,5 @@ def load():
 
 
 if __name__ == "__main__":
-    ok = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = build(sys.argv[1] if len(sys.argv) > 1 else REFERENCE)
     print("built" if ok else "reference checkout not found; nothing built")

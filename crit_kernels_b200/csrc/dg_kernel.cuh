@@ -60,8 +60,13 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 //   class 0   M small: the kernel is HBM-bound. 12 consumer + 4 producer warps (128 registers each): as many warps
 //             as the register file gives, to hide shared-memory and conversion latencies; every SM sub-partition
 //             hosts the same number of consumers.
-//   class 1   M medium: 10 consumer + 2 producer warps (168 registers each).
-//   class 2   M large: the kernel is FP32-FMA-bound. 6 consumer + 2 producer warps, 255 registers each.
+//   class 1   M medium: 11 consumer + 1 producer warps (168 registers each).
+//   class 2   M large: the kernel is FP32-FMA-bound. 7 consumer + 1 producer warps, 255 registers each.
+//             In classes 1 and 2 the consumers' instruction issue is the limit, a sub-partition's time is that of
+//             the consumers it hosts, and one warp keeps up with the copies: a single producer warp leaves only one
+//             sub-partition a consumer short (measured against 10 + 2 and 6 + 2: 4-8 % and 10-17 % faster). Measured
+//             slower: no producer warp at all with the consumers sharing the copies (12 + 0 and 8 + 0, 10-12 %),
+//             and the class limits moved either way (15-30 %).
 // Classes 0 and 1 hold the converted activations of a block and stream the rows past them; class 2 holds the rows'
 // decoded weights and streams the activation rows.
 // One warp issues a 1-D bulk copy only every ~60 clocks, so full groups of rows travel as one 2-D tensor copy and
@@ -71,11 +76,19 @@ __host__ __device__ constexpr int shape_class(int fmt, int m) {
 }
 __host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class(fmt, m) < 2; }
 // (BF16 weights, the lightest arithmetic per byte, measured 13-19 % faster with 14 + 2 warps than with 12 + 4.)
+#ifndef DG_C1_CW   // compile-time overrides, for tuning
+#define DG_C1_CW 11
+#define DG_C1_PW 1
+#endif
+#ifndef DG_C2_CW
+#define DG_C2_CW 7
+#define DG_C2_PW 1
+#endif
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12) : shape_class(fmt, m) == 1 ? 10 : 6;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12) : shape_class(fmt, m) == 1 ? DG_C1_CW : DG_C2_CW;
 }
 __host__ __device__ constexpr int producer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : 2;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : shape_class(fmt, m) == 1 ? DG_C1_PW : DG_C2_PW;
 }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }

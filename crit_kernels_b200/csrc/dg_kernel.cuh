@@ -5,13 +5,14 @@
 // :191 bf16_kernel, :285 fp8_kernel). Same formats, same contract (FP32 sums whose order never depends on the row
 // count), a different machine mapping:
 //
-//   * one persistent CTA per SM: C consumer warps + P producer warps (12 + 4 or 6 + 2, by format and M). The matrix
+//   * one persistent CTA per SM: C consumer warps + P producer warps (12 + 4 down to 8 + 0, by format and M). The matrix
 //     rows are split into one contiguous range per CTA; a range is walked in tiles of C*r rows (r rows per consumer
 //     warp) and each tile in K windows.
 //   * the producer warps stream every window of a tile into a shared-memory ring: one cp.async.bulk (TMA 1-D bulk
 //     copy, mbarrier complete_tx) per weight row (and per row of block scales), issued by the producers' lanes in
 //     parallel, plus the matching window of the activations as 16-byte cp.async copies into a bank-swizzled layout.
-//     Bytes in flight are set by the ring (up to ~200 KB per SM), not by registers.
+//     Bytes in flight are set by the ring (up to ~200 KB per SM), not by registers. Where the arithmetic, not HBM,
+//     is the limit (larger M) the CTA has no producer warp: its consumer warps issue the same copies between stages.
 //   * consumer warp w owns rows w, w+C, ... of the tile. Lane l owns the 16-byte blocks l, l+32, ... of each row and
 //     keeps two FP32 chains per (row, m): even and odd elements, advanced together by one packed fma.rn.f32x2. The
 //     chains visit the blocks in ascending order, the two chains are added, and one xor-shuffle tree (16, 8, 4, 2, 1)
@@ -60,13 +61,16 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 //   class 0   M small: the kernel is HBM-bound. 12 consumer + 4 producer warps (128 registers each): as many warps
 //             as the register file gives, to hide shared-memory and conversion latencies; every SM sub-partition
 //             hosts the same number of consumers.
-//   class 1   M medium: 11 consumer + 1 producer warps (168 registers each).
-//   class 2   M large: the kernel is FP32-FMA-bound. 7 consumer + 1 producer warps, 255 registers each.
-//             In classes 1 and 2 the consumers' instruction issue is the limit, a sub-partition's time is that of
-//             the consumers it hosts, and one warp keeps up with the copies: a single producer warp leaves only one
-//             sub-partition a consumer short (measured against 10 + 2 and 6 + 2: 4-8 % and 10-17 % faster). Measured
-//             slower: no producer warp at all with the consumers sharing the copies (12 + 0 and 8 + 0, 10-12 %),
-//             and the class limits moved either way (15-30 %).
+//   class 1   M medium: 11 consumer + 1 producer warps, or 12 consumer warps that issue the copies themselves
+//             (168 registers each).
+//   class 2   M large: the kernel is FP32-FMA-bound. 8 consumer warps, 255 registers each, no producer warp.
+//             In classes 1 and 2 the consumers' instruction issue is the limit and a sub-partition's time is that of
+//             the consumers it hosts, so the consumers should be spread evenly: one producer warp keeps up with the
+//             copies and leaves one sub-partition a consumer short (measured against 10 + 2 and 6 + 2 warps: 4-8 %
+//             and 10-17 % faster); no producer warp at all leaves none short but adds the copies to the consumers'
+//             instruction streams (measured against 11 + 1 and 7 + 1: class 2 up to 14 % faster, never slower;
+//             class 1 4-8 % faster for BF16 and MXFP8, 3-6 % slower for FP8 and NVFP4, which keep the producer).
+//             Moving the class limits either way measured 15-30 % slower.
 // Classes 0 and 1 hold the converted activations of a block and stream the rows past them; class 2 holds the rows'
 // decoded weights and streams the activation rows.
 // One warp issues a 1-D bulk copy only every ~60 clocks, so full groups of rows travel as one 2-D tensor copy and
@@ -76,19 +80,16 @@ __host__ __device__ constexpr int shape_class(int fmt, int m) {
 }
 __host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class(fmt, m) < 2; }
 // (BF16 weights, the lightest arithmetic per byte, measured 13-19 % faster with 14 + 2 warps than with 12 + 4.)
-#ifndef DG_C1_CW   // compile-time overrides, for tuning
-#define DG_C1_CW 11
-#define DG_C1_PW 1
-#endif
-#ifndef DG_C2_CW
-#define DG_C2_CW 7
-#define DG_C2_PW 1
-#endif
+// class 1 of the formats with the lighter arithmetic per byte (BF16, MXFP8) and class 2 of all: no producer warp.
+__host__ __device__ constexpr bool self_fed(int fmt, int m) {
+  return shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && (fmt == FMT_BF16 || fmt == FMT_MXFP8));
+}
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12) : shape_class(fmt, m) == 1 ? DG_C1_CW : DG_C2_CW;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12)
+         : shape_class(fmt, m) == 1 ? (self_fed(fmt, m) ? 12 : 11) : 8;
 }
 __host__ __device__ constexpr int producer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : shape_class(fmt, m) == 1 ? DG_C1_PW : DG_C2_PW;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : self_fed(fmt, m) ? 0 : 1;
 }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }
@@ -339,6 +340,10 @@ struct Producer {
   __device__ __forceinline__ Producer(const Params& p_, unsigned char* smem, uint32_t full0_, uint32_t empty0_, int pl_)
       : p(p_), wk(p_), lay(p_), ring(smem_addr(smem) + kSmemHeader), full0(full0_), empty0(empty0_),
         staged(SCB != 0 && p_.scale_mode == SCALES_STAGED), pl(pl_) {}
+  __device__ __forceinline__ Producer(const Params& p_, const Walk<CW>& wk_, const StageLayout<FMT, M, CW>& lay_,
+                                      unsigned char* smem, uint32_t full0_, uint32_t empty0_, int pl_)
+      : p(p_), wk(wk_), lay(lay_), ring(smem_addr(smem) + kSmemHeader), full0(full0_), empty0(empty0_),
+        staged(SCB != 0 && p_.scale_mode == SCALES_STAGED), pl(pl_) {}
 
   // Weight (and scale) copies of iteration `it` (tile it / nwin, window it % nwin) into stage s.
   // Full groups of CW rows travel as one 2-D tensor copy each (always the whole box: columns past the row's end are
@@ -395,6 +400,31 @@ struct Producer {
       }
     }
     cp_async_arrive_noinc(full);
+  }
+
+  // The same copies when all the CTA's threads share them (PL a multiple of a step's slots): a thread keeps one
+  // slot position of every step and every (PL / slots-per-step)-th activation row, so its addresses advance by
+  // constants.
+  __device__ __forceinline__ void activations_shared(int it, int s) const {
+    constexpr int STEP_SLOTS = 32 * NQ, MSTRIDE = PL / STEP_SLOTS;
+    static_assert(PL % STEP_SLOTS == 0 && MSTRIDE >= 1, "copying threads must cover whole steps");
+    const int win = it % wk.nwin;
+    const int byte0 = win * wk.win_bytes;
+    const int wbytes = min(wk.win_bytes, p.row_bytes - byte0);
+    const int slots = (wbytes >> 4) * NQ;
+    const int in_step = pl % STEP_SLOTS, m0 = pl / STEP_SLOTS;
+    uint32_t dst = ring + (uint32_t)s * p.stage_bytes + lay.x_off + swizzle_slot<NQ>(in_step) * 16;
+    const unsigned char* src =
+        reinterpret_cast<const unsigned char*>(p.x) + (size_t)(byte0 >> 4) * E * 2 + (size_t)in_step * 16;
+    const size_t xrow = (size_t)p.ldx * 2;
+    for (int sl = in_step; sl < slots; sl += STEP_SLOTS, dst += M * 64 * E, src += STEP_SLOTS * 16) {
+#pragma unroll
+      for (int k = 0; k < (M + MSTRIDE - 1) / MSTRIDE; ++k) {
+        const int m = m0 + k * MSTRIDE;
+        if (m < M) cp_async16(dst + m * (64 * E), src + m * xrow);
+      }
+    }
+    cp_async_arrive_noinc(full0 + 8u * s);
   }
 
   __device__ __forceinline__ void run(volatile int* abort_flag) const {
@@ -695,10 +725,26 @@ __device__ __forceinline__ int lane_value(int lane, int slot) {
 // ---------------------------------------------------------------------------------------------------------------
 // One tile for one consumer warp holding up to R rows (nr of them real).
 
-template <int FMT, int M, int R, typename XT, int CW>
+// SELF: the CTA has no producer warps; its consumer warps share the copies. A warp that has finished iteration `it`
+// (stage s) refills the stage of iteration it - 1, which every warp has probably left by then, with iteration
+// it + stages - 1: nobody waits for the slowest warp of the iteration just finished, and the ring runs one stage
+// short of its depth. All threads share the activation copies; the warps take turns with the weight copies.
+template <int FMT, int M, int CW>
+__device__ __forceinline__ void self_fill(const Params& p, const Walk<CW>& wk, const StageLayout<FMT, M, CW>& lay,
+                                          unsigned char* smem, uint32_t full0, uint32_t empty0, int it, int s,
+                                          bool with_weights, bool with_activations) {
+  const int warp = threadIdx.x >> 5;
+  if (with_weights && warp == it % CW)
+    Producer<FMT, M, CW, 1>(p, wk, lay, smem, full0, empty0, (int)(threadIdx.x & 31)).weights(it, s);
+  if (with_activations)
+    Producer<FMT, M, CW, CW>(p, wk, lay, smem, full0, empty0, (int)threadIdx.x).activations_shared(it, s);
+}
+
+template <int FMT, int M, int R, typename XT, int CW, bool SELF>
 __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk, const StageLayout<FMT, M, CW>& lay,
                                              unsigned char* smem, uint32_t full0, uint32_t empty0,
-                                             volatile int* abort_flag, int row0, int nr, int& s, uint32_t& parity) {
+                                             volatile int* abort_flag, int row0, int nr, int& s, uint32_t& parity,
+                                             int& it) {
   constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
   constexpr bool FEW = few_rows(FMT, M);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -770,6 +816,15 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8u * s);
+    if constexpr (SELF) {
+      const int next = it + p.stages - 1;
+      if (next < wk.ntiles * wk.nwin) {
+        const int sp = s == 0 ? p.stages - 1 : s - 1;   // stage of iteration it - 1 (never used yet when it = 0)
+        if (it > 0 && !mbar_wait(empty0 + 8u * sp, s == 0 ? parity ^ 1u : parity, abort_flag)) return false;
+        self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, next, sp, true, true);
+      }
+    }
+    ++it;
     if (++s == p.stages) { s = 0; parity ^= 1u; }
   }
 
@@ -867,12 +922,14 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
     gemv_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int RMAX = rows_max(FMT, M), CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);
+  constexpr bool SELF = PW == 0;             // no producer warps: the consumers issue the copies themselves
+  constexpr int COPY_WARPS = SELF ? CW : PW;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
   const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full0 + 8u * s, 32 * PW + 1);           // the producers' cp.async arrivals + the expect_tx arrival
+      mbar_init(full0 + 8u * s, 32 * COPY_WARPS + 1);   // the copying lanes' cp.async arrivals + the expect_tx arrival
       mbar_init(empty0 + 8u * s, CW);
     }
     *abort_flag = 0;
@@ -884,12 +941,24 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
 
   const int warp = threadIdx.x >> 5;
   if (warp >= CW) {
-    Producer<FMT, M, CW, PW>(p, smem, full0, empty0, (int)threadIdx.x - CW * 32).run(abort_flag);
+    if constexpr (!SELF)
+      Producer<FMT, M, CW, COPY_WARPS>(p, smem, full0, empty0, (int)threadIdx.x - CW * 32).run(abort_flag);
   } else {
-    griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
     const Walk<CW> wk(p);
     const StageLayout<FMT, M, CW> lay(p);
-    int s = 0;
+    if constexpr (SELF) {
+      // the first stages - 1 iterations; with static weights their weight copies leave before the previous kernel
+      // of the stream has completed
+      const int first = min(p.stages - 1, wk.ntiles * wk.nwin);
+      if (p.early_weights)
+        for (int i = 0; i < first; ++i) self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, i, true, false);
+      griddep_wait();
+      for (int i = 0; i < first; ++i)
+        self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, i, !p.early_weights, true);
+    } else {
+      griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
+    }
+    int s = 0, it = 0;
     uint32_t parity = 0;
     bool ok = true;
     for (int t = 0; t < wk.ntiles && ok; ++t) {
@@ -897,11 +966,14 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
       const int rows = min(wk.tile_rows, wk.hi - row0);
       const int nr = rows > warp ? (rows - warp + CW - 1) / CW : 0;
       if (nr > 2)
-        ok = consume_tile<FMT, M, RMAX, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
+        ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
+                                                      it);
       else if (nr > 1)
-        ok = consume_tile<FMT, M, 2, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
+        ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
+                                                      it);
       else
-        ok = consume_tile<FMT, M, 1, XT, CW>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity);
+        ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
+                                                      it);
     }
     if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
     if (p.world >= 1) gather_finish<M, CW>(p, abort_flag);

@@ -314,7 +314,8 @@ def test_one_rank_allgather_is_the_plain_gemv():
     assert cabi.load().dg_take_status() == 0
 
 
-def test_static_weight_prefetch_gives_the_same_bits():
+@pytest.mark.parametrize("m", [4, 9])   # kernels with producer warps; kernels whose consumers issue the copies
+def test_static_weight_prefetch_gives_the_same_bits(m):
     """dg_set_static_weights(1) lets a GEMV stream weights before the previous kernel of the stream has finished; the
     results of back-to-back GEMVs whose activations are the previous GEMV's outputs stay bit-identical."""
     from crit_kernels_b200 import cabi
@@ -323,12 +324,12 @@ def test_static_weight_prefetch_gives_the_same_bits():
     c1, s1, i1 = cuda(*wl.cfg_nvfp4(n, n, seed=1))
     c2, s2, i2 = cuda(*wl.cfg_nvfp4(n, n, seed=2))
     fc, fs = cuda(*wl.cfg_fp8(n, n, seed=3))
-    x = wl.activations(4, n).to(dev)
+    x = wl.activations(m, n).to(dev)
 
     def chain():
-        a = torch.empty(4, n, dtype=torch.bfloat16, device=dev)
-        b = torch.empty(4, n, dtype=torch.bfloat16, device=dev)
-        c = torch.empty(4, n, dtype=torch.bfloat16, device=dev)
+        a = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        b = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         for _ in range(3):                      # each GEMV reads what the one before it wrote
             k.gemv(x, c1, s1, i1, a)
             k.gemv(a, c2, s2, i2, b)

@@ -18,6 +18,7 @@ SIGNATURES = {
     "dg_enqueue_gather_wait": (_i, [_p, _i, ctypes.c_uint, _p]),
     "dg_enqueue_fp8": (_i, [_p, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dg_enqueue_dequantize": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
     "dg_hardware_decode": (_i, []),
     "dg_plan": (_i, [_i, _i, _i, _i, _f]),
     "dg_take_status": (_i, []),

@@ -4,8 +4,9 @@ row's result is the same bits alone and beside the other rows of a call, and the
 matrix's rows: the summation order depends on K and the format only.
 
 Same functions, argument layouts and refusals as the reference package's CUDA entry points
-(decode-gemv/torch-ext/decode_gemv/__init__.py:19-53). The reference's Triton entry points (gemv_triton, decode,
-decode_fp8, gemv_fp8_dot, ...) are not part of this package.
+(decode-gemv/torch-ext/decode_gemv/__init__.py:19-53), plus the NVFP4 dequantizers decode and decode_fp8, which the
+reference implements in Triton (triton_gemv.py:171-200) and this package in CUDA. The reference's other Triton entry
+points (gemv_triton, gemv_fp8_dot, ...) are not part of this package.
 
 NVFP4 matrices as checkpoints store them: codes [N][K / 2] uint8 (element 2i in the low nibble of byte i), E4M3 block
 scales [N][K / 16] (row major, or cuBLASLt's 128 x 4 tiles with blocked=True) and inverse [N] FP32 (one over each row's
@@ -16,10 +17,10 @@ from ._ops import ops
 
 CUDA_ROWS = 16   # rows the GEMVs take in one call
 
-__all__ = ["CUDA_ROWS", "gemv", "gemv_fp8", "gemv_bf16", "hardware_decode"]
+__all__ = ["CUDA_ROWS", "gemv", "gemv_fp8", "gemv_bf16", "hardware_decode", "decode", "decode_fp8"]
 
 _TRITON_SIDE = {"DOT_ROWS", "TRITON_ROWS", "dot_partial_elements", "fp8_dot_tile", "gemv_fp8_dot", "gemv_triton",
-                "decode", "decode_fp8", "hardware"}
+                "hardware"}
 
 
 def gemv(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, inverse: torch.Tensor, out: torch.Tensor,
@@ -52,8 +53,27 @@ def hardware_decode(device=None) -> bool:
     return bool(ops.hardware_decode(torch.empty(0, device=device)))
 
 
+def decode(codes: torch.Tensor, scales: torch.Tensor, inverse: torch.Tensor, out: torch.Tensor):
+    """The NVFP4 matrix's values [N][K] in out's dtype (BF16 or FP16, contiguous): e2m1 * scale * inverse, one FP32
+    product rounded once. codes [N][K / 2] uint8, scales [N][K / 16] E4M3 (row major), inverse [N] FP32. Returns
+    out."""
+    if out.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError(f"decode: out must be BF16 or FP16, got {out.dtype} (decode_fp8 writes FP8 E4M3)")
+    ops.decode(codes, scales, inverse, out)
+    return out
+
+
+def decode_fp8(codes: torch.Tensor, scales: torch.Tensor, factor: torch.Tensor, out: torch.Tensor):
+    """The NVFP4 matrix's values [N][K] as FP8 E4M3 (out contiguous float8_e4m3fn) in units of each row's scale: e2m1 *
+    scale * factor[row], rounded once to nearest even within +-448. Returns out."""
+    if out.dtype != torch.float8_e4m3fn:
+        raise RuntimeError(f"decode_fp8: out must be float8_e4m3fn, got {out.dtype}")
+    ops.decode(codes, scales, factor, out)
+    return out
+
+
 def __getattr__(name):
     if name in _TRITON_SIDE:
         raise AttributeError(f"decode_gemv.{name} is one of the reference's Triton entry points; this B200 package "
-                             "provides the CUDA GEMVs only (gemv, gemv_fp8, gemv_bf16, hardware_decode)")
+                             "provides CUDA kernels only (gemv, gemv_fp8, gemv_bf16, hardware_decode, decode, decode_fp8)")
     raise AttributeError(name)

@@ -1,6 +1,7 @@
 // Torch op registration and argument checks over the C ABI (include/decode_gemv_b200.h).
 //
-// The schemas are those of the reference (decode-gemv/torch-ext/torch_binding.cpp:7-10), CUDA implementations only,
+// The GEMV schemas are those of the reference (decode-gemv/torch-ext/torch_binding.cpp:7-10; `decode`, the NVFP4
+// dequantizer, is a Triton function there and an op only here), CUDA implementations only,
 // and every refusal of its entry points (decode-gemv/decode_gemv_cuda/binding.cu:19-118) is kept: a violated rule
 // raises c10::Error, a Python RuntimeError. Nothing here allocates or waits for the device, and the launch goes to
 // the current stream of x's device, so a CUDA graph captures the calls.
@@ -137,6 +138,35 @@ void gemv_bf16(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& ou
                   op);
 }
 
+void decode(const torch::Tensor& codes, const torch::Tensor& scales, const torch::Tensor& factor,
+            torch::Tensor& out) {
+  const char* op = "decode";
+  TORCH_CHECK(out.is_cuda() && out.dim() == 2 && out.is_contiguous() && on_boundary(out, 16), op,
+              ": out must be a contiguous 2-D CUDA tensor [N][K] on a 16-byte boundary");
+  const auto type = out.scalar_type();
+  const int kind = type == torch::kBFloat16 ? 1 : type == torch::kFloat16 ? 2 : type == torch::kFloat8_e4m3fn ? 3 : 0;
+  TORCH_CHECK(kind != 0, op, ": out must be BF16, FP16 or FP8 E4M3, got ", type);
+  const int64_t n = out.size(0), k = out.size(1);
+  TORCH_CHECK(n >= 1 && k >= 16 && k % 16 == 0, op, ": out must be [N][K] with K a multiple of 16, got [", n, "][", k,
+              "]");
+  TORCH_CHECK(codes.is_cuda() && codes.dim() == 2 && codes.is_contiguous() && codes.scalar_type() == torch::kUInt8 &&
+                  codes.size(0) == n && codes.size(1) * 2 == k && on_boundary(codes, 16),
+              op, ": codes must be contiguous uint8 [N][K / 2] on a 16-byte boundary");
+  TORCH_CHECK(scales.is_cuda() && scales.is_contiguous() && scales.element_size() == 1 && scales.dim() == 2 &&
+                  scales.size(0) == n && scales.size(1) * 16 == k,
+              op, ": scales must be contiguous E4M3 bytes [N][K / 16]");
+  TORCH_CHECK(factor.is_cuda() && factor.is_contiguous() && factor.scalar_type() == torch::kFloat32 &&
+                  factor.numel() == n && on_boundary(factor, 4),
+              op, ": the per-row factor must be contiguous FP32 [N]");
+  require_same_device(out, {&codes, &scales, &factor}, op);
+  const c10::cuda::CUDAGuard guard(out.device());
+  require_success(dg_enqueue_dequantize(codes.data_ptr<std::uint8_t>(),
+                                        static_cast<const std::uint8_t*>(scales.data_ptr()), factor.data_ptr<float>(),
+                                        out.data_ptr(), kind, static_cast<int>(n), static_cast<int>(k),
+                                        at::cuda::getCurrentCUDAStream().stream()),
+                  op);
+}
+
 int64_t hardware_decode(const torch::Tensor& device_of) {
   const c10::cuda::CUDAGuard guard(device_of.device());
   return dg_hardware_decode();
@@ -147,6 +177,7 @@ TORCH_LIBRARY(DG_TORCH_NAMESPACE, ops) {
   ops.def("gemv_fp8(Tensor x, Tensor codes, Tensor scales, Tensor! out) -> ()");
   ops.def("gemv_bf16(Tensor x, Tensor w, Tensor! out) -> ()");
   ops.def("hardware_decode(Tensor device_of) -> int");
+  ops.def("decode(Tensor codes, Tensor scales, Tensor factor, Tensor! out) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(DG_TORCH_NAMESPACE, CUDA, ops) {
@@ -154,4 +185,5 @@ TORCH_LIBRARY_IMPL(DG_TORCH_NAMESPACE, CUDA, ops) {
   ops.impl("gemv_fp8", &gemv_fp8);
   ops.impl("gemv_bf16", &gemv_bf16);
   ops.impl("hardware_decode", &hardware_decode);
+  ops.impl("decode", &decode);
 }

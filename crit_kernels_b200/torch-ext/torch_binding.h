@@ -14,3 +14,7 @@ void gemv_fp8(const torch::Tensor& x, const torch::Tensor& codes, const torch::T
 void gemv_bf16(const torch::Tensor& x, const torch::Tensor& w, torch::Tensor& out);
 // 1: E2M1 decodes by the hardware conversion on device_of's device (always, for this sm_100a build).
 int64_t hardware_decode(const torch::Tensor& device_of);
+// The NVFP4 matrix's values into out [N][K] (contiguous BF16, FP16 or FP8 E4M3): e2m1 * scale * factor[row], one FP32
+// product rounded once (FP8: saturating at +-448). codes [N][K / 2] uint8, scales [N][K / 16] E4M3 bytes, factor [N]
+// FP32. The reference's decode and decode_fp8 (decode-gemv/torch-ext/decode_gemv/triton_gemv.py:171-176, :195-200).
+void decode(const torch::Tensor& codes, const torch::Tensor& scales, const torch::Tensor& factor, torch::Tensor& out);

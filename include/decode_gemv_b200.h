@@ -97,6 +97,16 @@ DG_API int dg_enqueue_fp8(const void* x, int ldx, int x_is_bf16, const uint8_t* 
 DG_API int dg_enqueue_bf16(const void* x, int ldx, const void* w, void* out, int ldo, int out_kind, int M, int N, int K,
                     void* stream);
 
+/* NVFP4 dequantizer: the matrix's values [N][K], contiguous, as BF16 (out_kind 1), FP16 (2) or FP8 E4M3 (3):
+ * e2m1(code) * scale (exact in FP32) times factor[row], one FP32 product, rounded once to the output type; the FP8
+ * form saturates at +-448 (the row's values in units of the caller's per-row scale, factor = inverse / that scale).
+ * Replaces the reference package's Triton dequantizers decode and decode_fp8 (torch-ext/decode_gemv/
+ * triton_gemv.py:171-176 and :195-200, kernels :156-168 and :179-192; contract pinned by
+ * tests/test_decode_gemv.py:131-140). codes [N][K/2] and out on 16 bytes, scales [N][K/16] E4M3 row-major,
+ * factor [N] FP32, K % 16 == 0, K >= 16, N >= 1. No allocation, no host synchronisation. */
+DG_API int dg_enqueue_dequantize(const uint8_t* codes, const uint8_t* scales, const float* factor, void* out,
+                                 int out_kind, int N, int K, void* stream);
+
 /* 1 when the current device runs this build's hardware E2M1 conversion (cvt.rn.f16x2.e2m1x2; always, on the sm_100a
  * target this library is built for), -1 when the current device cannot run the library. Replaces hardware_decode
  * (decode_gemv.h:43, decode_gemv.cu:419-427); unlike it, allocates nothing and launches nothing. */

@@ -55,6 +55,16 @@ def main():
         out[f"nvfp4_{tag}_values"] = v.numpy()
         out[f"nvfp4_{tag}_exact"] = (x.double() @ v.t()).numpy()
         out[f"nvfp4_{tag}_blocked"] = ref["to_blocked"](s.view(torch.uint8)).numpy()
+        # what the reference's test expects of its dequantizers decode / decode_fp8 (test_decode_gemv.py:131-140)
+        if tag == "c":
+            continue
+        unit = ref["values"](c, s, torch.ones_like(i)).float()
+        product = unit * i[:, None]
+        out[f"nvfp4_{tag}_decode_bf16"] = product.to(torch.bfloat16).view(torch.int16).numpy()
+        out[f"nvfp4_{tag}_decode_f16"] = product.to(torch.float16).view(torch.int16).numpy()
+        factor = i * 64
+        out[f"nvfp4_{tag}_decode_fp8"] = (unit * factor[:, None]).clamp(-448, 448).to(torch.float8_e4m3fn) \
+            .view(torch.uint8).numpy()
     for tag, (n, k, m, mx) in {"row": (96, 256, 16, False), "mx": (70, 512, 7, True)}.items():
         c, s = ref["fp8_matrix"](n, k, mx)
         x = ref["activations"](m, k)

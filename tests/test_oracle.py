@@ -102,3 +102,31 @@ def test_weight_bytes_of_the_configurations():
     assert wl.weight_bytes("mxfp8", 13824, 5120) == 72_990_720
     assert wl.weight_bytes("bf16", 8192, 8192) == 134_217_728
     assert sum(wl.weight_bytes("nvfp4", n, k) for _, k, n in wl.STACK_ROLES) == 481_632_256
+
+
+# ----- the dequantizers -------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_dequantize_matches_the_reference_tests_expectation(golden, tag):
+    """oracle.dequantize against what decode-gemv/tests/test_decode_gemv.py:131-140 expects of decode / decode_fp8
+    (golden vectors made from that expression on the reference's own generators)."""
+    g = golden
+    c, s, i = g[f"nvfp4_{tag}_codes"], g[f"nvfp4_{tag}_scales"], g[f"nvfp4_{tag}_inverse"]
+    bf = oc.dequantize(c, s, i, torch.bfloat16)
+    assert np.array_equal(bf.view(torch.int16).numpy(), g[f"nvfp4_{tag}_decode_bf16"])
+    fp = oc.dequantize(c, s, i, torch.float16)
+    assert np.array_equal(fp.view(torch.int16).numpy(), g[f"nvfp4_{tag}_decode_f16"])
+    f8 = oc.dequantize(c, s, i * np.float32(64), torch.float8_e4m3fn)
+    assert np.array_equal(f8.view(torch.uint8).numpy(), g[f"nvfp4_{tag}_decode_fp8"])
+
+
+def test_dequantize_saturates_and_rounds_once():
+    codes = np.array([[0x77, 0xF7, 0x21, 0x00, 0x10, 0x01, 0x99, 0xAB]], dtype=np.uint8)     # 16 values, one block
+    scales = np.array([[0x7E]], dtype=np.uint8)                                                # E4M3 448
+    out = oc.dequantize(codes, scales, np.array([1.0], dtype=np.float32), torch.float8_e4m3fn).float().numpy()
+    assert out.max() == 448.0 and out.min() == -448.0                                          # 6 * 448 clamps
+    third = np.array([1.0 / 3.0], dtype=np.float32)
+    bf = oc.dequantize(codes, np.array([[0x38]], dtype=np.uint8), third, torch.bfloat16)      # scale 1.0
+    want = torch.from_numpy(oc.nvfp4_values(codes, np.array([[0x38]], dtype=np.uint8), np.ones(1, np.float32))
+                            .astype(np.float32) * third[:, None]).to(torch.bfloat16)
+    assert torch.equal(bf, want)

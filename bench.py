@@ -9,7 +9,8 @@ Workloads
          call on its own copy of the weights (5 x 235 MB in rotation, so nothing is served from the 126 MB L2). The
          timed region replays a CUDA graph of the step (the reference's own method for its published numbers).
   stack  (N > 1 default) the 70B-shaped NVFP4 projection stack: 80 layers x {qkv, o, gate_up, down}, output columns
-         sharded over the ranks, every GEMV followed by an NCCL all-gather of its [M][N/P] outputs; a step = one pass
+         sharded over the ranks, every GEMV with the all-gather of its [M][N/P] outputs in its epilogue (peer stores over
+         NVLink; `--gather nccl` runs an NCCL all-gather after every GEMV instead); a step = one pass
          over the stack at each M in {1, 8, 16}, each pass one CUDA-graph replay. Total work is fixed ("strong").
 
 The line printed by rank 0 carries: `value` (device-timed, inputs resident in HBM), `e2e` (the same step through the

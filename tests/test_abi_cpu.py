@@ -76,3 +76,23 @@ def test_package_surface_matches_the_reference():
     schema = str(torch.ops._decode_gemv_b200.gemv.default._schema)
     assert schema.startswith("_decode_gemv_b200::gemv(Tensor x, Tensor codes, Tensor scales, Tensor inverse, "
                              "bool blocked, Tensor(") and schema.endswith(" out) -> ()") and "!" in schema
+
+
+def test_dequantizer_wrappers_refuse_wrong_output_types_before_any_device_work():
+    """decode writes 16-bit outputs, decode_fp8 FP8 E4M3: the other types are refused by the package functions
+    themselves (no GPU needed to see it)."""
+    import torch
+    import crit_kernels_b200
+    k = crit_kernels_b200.get_kernel("crit-labs/decode-gemv", version=1)
+    c = torch.zeros(2, 8, dtype=torch.uint8)
+    s = torch.zeros(2, 1, dtype=torch.uint8)
+    f = torch.ones(2)
+    with pytest.raises(RuntimeError):
+        k.decode(c, s, f, torch.empty(2, 16, dtype=torch.float32))
+    with pytest.raises(RuntimeError):
+        k.decode(c, s, f, torch.empty(2, 16, dtype=torch.float8_e4m3fn))
+    with pytest.raises(RuntimeError):
+        k.decode_fp8(c, s, f, torch.empty(2, 16, dtype=torch.bfloat16))
+    assert {"decode", "decode_fp8"} <= set(k.__all__)
+    with pytest.raises(AttributeError):
+        k.gemv_triton

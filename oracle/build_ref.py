@@ -1,6 +1,7 @@
 """TEST INFRASTRUCTURE ONLY. Builds oracle/_ref/libdecode_gemv_ref.so: the reference's own CUDA source
 (decode-gemv/decode_gemv_cuda/decode_gemv.cu, two files, no build system) compiled for sm_100a from where it lies in
-the reference checkout, plus oracle/ref_shim.cu. No reference source is copied; only the binary lands in oracle/_ref/
+the reference checkout, plus oracle/ref_shim.cu; and oracle/_ref/ref_host_check, a small program over the reference's
+header-only C++ host oracle (see build_host_check). No reference source is copied; only binaries land in oracle/_ref/
 (git-ignored, shipped to the GPU box). Without the checkout this is a no-op and whatever was built earlier is used.
 
     python -m oracle.build_ref [path/to/reference]
@@ -37,6 +38,27 @@ def build(reference=REFERENCE, verbose=True):
     return True
 
 
+HOST_CHECK = os.path.join(OUT_DIR, "ref_host_check")
+
+
+def build_host_check(reference=REFERENCE, verbose=True):
+    """oracle/_ref/ref_host_check: oracle/ref_host_check.cpp over the reference's header-only C++ host oracle
+    (fp8-block-rows/tests/order/row_fp8.h, fp8_block.h), included from where it lies. g++ -std=c++20, no other
+    dependency. Used by tests/golden/make_golden.py only."""
+    inc = os.path.join(reference, "fp8-block-rows", "tests", "order")
+    src = os.path.join(HERE, "ref_host_check.cpp")
+    if not os.path.exists(os.path.join(inc, "row_fp8.h")):
+        return os.path.exists(HOST_CHECK)
+    if os.path.exists(HOST_CHECK) and os.path.getmtime(HOST_CHECK) > os.path.getmtime(src):
+        return True
+    os.makedirs(OUT_DIR, exist_ok=True)
+    cmd = ["g++", "-std=c++20", "-O2", f"-I{inc}", src, "-o", HOST_CHECK]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+    return True
+
+
 def load():
     """The reference library, or None when it was never built."""
     if not os.path.exists(LIB):
@@ -53,4 +75,5 @@ def load():
 
 if __name__ == "__main__":
     ok = build(sys.argv[1] if len(sys.argv) > 1 else REFERENCE)
+    build_host_check(sys.argv[1] if len(sys.argv) > 1 else REFERENCE)
     print("built" if ok else "reference checkout not found; nothing built")

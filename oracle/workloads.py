@@ -69,15 +69,29 @@ def cfg_fp8(n, k, seed=1):
     return codes, scales
 
 
+def mx_shared_exponent(amax):
+    """The MX shared exponent of groups with these maxima: floor(log2(amax)) - 8, 0 for an all-zero group, kept in
+    [-127, 127]: the reference's rule (fp8-block-rows/tests/order/fp8_block.h:28-33, frexp(amax) - 1 - 8)."""
+    _, e = torch.frexp(amax.float())                       # amax = m * 2^e with m in [0.5, 1)
+    shared = torch.where(amax > 0, e - 1 - 8, torch.zeros_like(e))
+    return shared.clamp(-127, 127).float()
+
+
+def mx_quantize(w):
+    """[..., 32] FP32 groups -> (E4M3 codes as uint8 [..., 32], E8M0 bytes [...]): codes = E4M3(w / 2^shared), nearest
+    even, saturating at +-448 (a torch cast above 448 would give NaN, hence the clamp)."""
+    shared = mx_shared_exponent(w.abs().amax(dim=-1))
+    codes = (w / torch.exp2(shared)[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return codes.view(torch.uint8), (shared + 127).to(torch.uint8)
+
+
 def cfg_mxfp8(n, k, seed=2):
     """MXFP8 of N(0, 0.02) weights: per 32 inputs shared = floor(log2(amax)) - 8, byte = shared + 127, codes =
-    E4M3(w / 2^shared) clamped to +-448 (a torch cast above 448 would give NaN)."""
+    E4M3(w / 2^shared)."""
     g = _gen(seed)
     w = (torch.randn(n, k, generator=g) * 0.02).view(n, k // 32, 32)
-    amax = w.abs().amax(dim=-1).clamp_min(2.0 ** -120)
-    shared = torch.floor(torch.log2(amax)) - 8
-    codes = (w / torch.exp2(shared)[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn)
-    return codes.view(n, k).view(torch.uint8), (shared + 127).to(torch.uint8)
+    codes, mx = mx_quantize(w)
+    return codes.view(n, k), mx
 
 
 def cfg_bf16(n, k, seed=3):

@@ -130,3 +130,40 @@ def test_dequantize_saturates_and_rounds_once():
     want = torch.from_numpy(oc.nvfp4_values(codes, np.array([[0x38]], dtype=np.uint8), np.ones(1, np.float32))
                             .astype(np.float32) * third[:, None]).to(torch.bfloat16)
     assert torch.equal(bf, want)
+
+
+# ----- the reference's C++ host oracle (row_fp8.h, fp8_block.h) ---------------------------------------------------
+
+def test_e4m3_decode_matches_the_reference_host_oracle(golden):
+    """crit::fp8::decode (fp8-block-rows/tests/order/row_fp8.h:25-31) for every byte it accepts."""
+    mine = oc.e4m3_to_float(np.arange(256, dtype=np.uint8))
+    want = golden["host_decode"].astype(np.float64)
+    ok = ~np.isnan(want)
+    assert ok.sum() == 254 and np.array_equal(mine[ok], want[ok])
+    assert np.array_equal(np.signbit(mine[ok]), np.signbit(want[ok])) and np.isnan(mine[~ok]).all()
+
+
+def test_fp8_projection_matches_the_reference_host_oracle(golden):
+    """crit::fp8::project (row_fp8.h:86-98): FP64 projection of E4M3 codes with BF16 row scales and BF16 activations,
+    against the Python oracle's stored values and exact product (summation order differs: 1e-12)."""
+    def bf16(words):
+        return torch.from_numpy(words.astype(np.int16)).view(torch.bfloat16)
+    codes = golden["host_codes"]
+    scales = bf16(golden["host_scales_bf16"]).float()
+    x = bf16(golden["host_x_bf16"])
+    mine = oc.gemv_exact(x, oc.fp8_values(codes, scales)).numpy()
+    want = golden["host_project"]
+    assert np.allclose(mine, want, rtol=1e-12, atol=1e-300)
+
+
+def test_mx_groups_match_the_reference_host_quantizer(golden):
+    """crit::fp8_block::quantize_group, MX kind (fp8_block.h:24-39): the shared exponent and the E4M3 codes of the
+    workload generator's MXFP8 groups, and e8m0 (fp8_block.h:18-21) against the oracle's E8M0 decode."""
+    values = torch.from_numpy(golden["host_mx_values"])
+    codes, mx = wl.mx_quantize(values)
+    scale = oc.e8m0_to_float(mx.numpy())
+    assert np.array_equal(scale, golden["host_mx_scale"].astype(np.float64))
+    assert np.array_equal(scale, golden["host_mx_e8m0"].astype(np.float64))
+    assert np.array_equal(codes.numpy() & 127, golden["host_mx_codes"] & 127)                 # magnitudes
+    nonzero = (golden["host_mx_codes"] & 127) != 0
+    assert np.array_equal((codes.numpy() & 128)[nonzero], (golden["host_mx_codes"] & 128)[nonzero])

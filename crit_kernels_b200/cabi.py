@@ -23,6 +23,7 @@ SIGNATURES = {
     "dg_plan": (_i, [_i, _i, _i, _i, _f]),
     "dg_take_status": (_i, []),
     "dg_set_static_weights": (_i, [_i]),
+    "dg_set_trace": (_i, [_p, _i]),
     "dg_version": (_i, []),
 }
 FMT = {"bf16": 0, "fp8": 1, "mxfp8": 2, "nvfp4": 3}

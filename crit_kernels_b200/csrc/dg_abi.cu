@@ -59,6 +59,9 @@ bool encode_rows(CUtensorMap* map, const void* base, int rows, int row_bytes, in
 }
 DeviceState g_devices[kMaxDevices];
 std::atomic<int> g_static_weights{0};   // dg_set_static_weights
+// dg_set_trace: launch i of the GEMV kernels (counted from the call that set the buffer) stamps into region i
+std::atomic<unsigned long long*> g_trace_base{nullptr};
+std::atomic<int> g_trace_capacity{0}, g_trace_next{0};
 
 const void* const* const kTables[] = {dg_table_bf16,       dg_table_fp8_bf16,   dg_table_fp8_f16,  dg_table_mxfp8_bf16,
                                       dg_table_mxfp8_f16,  dg_table_nvfp4_bf16, dg_table_nvfp4_f16};
@@ -158,6 +161,11 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   if (p.use_2d && p.scale_mode == dg::SCALES_STAGED)
     p.use_2d = encode_rows(&p.tmap_sc, p.scales, p.N, p.scale_row_bytes, cw, p.steps * kFormats[fmt].scb);
   p.early_weights = g_static_weights.load(std::memory_order_relaxed);
+  if (unsigned long long* base = g_trace_base.load(std::memory_order_acquire)) {
+    const int index = g_trace_next.fetch_add(1, std::memory_order_relaxed);
+    if (index < g_trace_capacity.load(std::memory_order_relaxed))
+      p.trace = base + (size_t)index * DG_TRACE_CTAS * dg::kTraceSlots;
+  }
   void* args[] = {&p};
   const int threads = 32 * (dg::consumer_warps(fmt, M) + dg::producer_warps(fmt, M));
   // Programmatic dependent launch: the kernel may start while the previous kernel of the stream drains (its launch,
@@ -358,6 +366,14 @@ int dg_set_static_weights(int enabled) {
   return g_static_weights.exchange(enabled ? 1 : 0, std::memory_order_relaxed);
 }
 
-int dg_version(void) { return 101; }
+int dg_set_trace(void* buffer, int launches) {
+  g_trace_base.store(nullptr, std::memory_order_release);
+  g_trace_next.store(0, std::memory_order_relaxed);
+  g_trace_capacity.store(buffer && launches > 0 ? launches : 0, std::memory_order_relaxed);
+  if (buffer && launches > 0) g_trace_base.store(static_cast<unsigned long long*>(buffer), std::memory_order_release);
+  return 0;
+}
+
+int dg_version(void) { return 102; }
 
 }  // extern "C"

@@ -49,6 +49,10 @@ constexpr int kStatusProducerTimeout = 1;
 constexpr int kStatusConsumerTimeout = 2;
 constexpr int kStatusGatherTimeout = 4;
 constexpr int kMaxRanks = 8;
+// Time stamps (%globaltimer, ns) a CTA leaves in Params::trace when a trace buffer is set: kernel entry, the wait for
+// the previous kernel of the stream passed, first stage full, last stage consumed, last warp done; then the SM id.
+constexpr int kTraceSlots = 8;
+enum : int { TRACE_ENTRY = 0, TRACE_DEP = 1, TRACE_FIRST_FULL = 2, TRACE_LAST_CONSUMED = 3, TRACE_EXIT = 4, TRACE_SM = 5 };
 
 template <int FMT> struct Format;
 template <> struct Format<FMT_BF16>  { static constexpr int E = 8,  SCB = 0;  };   // elements / scale bytes per
@@ -114,6 +118,7 @@ struct Params {
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
   int early_weights;         // 1: weight copies may be issued before the previous kernel of the stream completed
+  unsigned long long* trace; // diagnostic (dg_set_trace): kTraceSlots time stamps per CTA, or null
   // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results go into slot `rank` of its own
   // [world][M][N] buffer; every CTA then copies its rows to the same slot of every other rank's buffer (peer_out[q],
   // peer-mapped addresses) and counts itself done in word 2 of this rank's counter block; the last CTA adds 1 to
@@ -206,6 +211,9 @@ __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+__device__ __forceinline__ void trace_stamp(unsigned long long* trace, int slot) {   // the latest stamp of a slot wins
+  if (trace) atomicMax(trace + (size_t)blockIdx.x * kTraceSlots + slot, global_ns());
 }
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const unsigned long long start = global_ns();
@@ -768,6 +776,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
 
   for (int win = 0; win < wk.nwin; ++win) {
     if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;
+    if (it == 0 && threadIdx.x == 0) trace_stamp(p.trace, TRACE_FIRST_FULL);
     if (nr > 0) {
       const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
       const int blk0 = win * p.steps * 32;
@@ -928,6 +937,12 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
   const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
   if (threadIdx.x == 0) {
+    if (p.trace) {
+      unsigned int sm;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+      p.trace[(size_t)blockIdx.x * kTraceSlots + TRACE_SM] = sm;
+      trace_stamp(p.trace, TRACE_ENTRY);
+    }
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(full0 + 8u * s, 32 * COPY_WARPS + 1);   // the copying lanes' cp.async arrivals + the expect_tx arrival
       mbar_init(empty0 + 8u * s, CW);
@@ -958,6 +973,7 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
     } else {
       griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
     }
+    if (threadIdx.x == 0) trace_stamp(p.trace, TRACE_DEP);
     int s = 0, it = 0;
     uint32_t parity = 0;
     bool ok = true;
@@ -976,8 +992,10 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
                                                       it);
     }
     if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
+    if ((threadIdx.x & 31) == 0) trace_stamp(p.trace, TRACE_LAST_CONSUMED);
     if (p.world >= 1) gather_finish<M, CW>(p, abort_flag);
   }
+  if ((threadIdx.x & 31) == 0) trace_stamp(p.trace, TRACE_EXIT);
   // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
   // memory is handed to the next one (bounded sleep, error path only).
   if (*abort_flag) {

@@ -131,6 +131,17 @@ DG_API int dg_take_status(void);
  * any caller. Process-wide; returns the previous setting. No counterpart in the reference. */
 DG_API int dg_set_static_weights(int enabled);
 
+/* Diagnostic: where a launch's time goes. `buffer` is zero-filled device memory for `launches` regions of
+ * DG_TRACE_CTAS x DG_TRACE_SLOTS 64-bit words; the i-th GEMV launch after this call (any stream, any format) leaves
+ * per CTA c, at word (i * DG_TRACE_CTAS + c) * DG_TRACE_SLOTS + s, the %globaltimer value (ns) at which: s = 0 the
+ * CTA started, 1 its wait for the previous kernel of the stream ended, 2 its first ring stage was full, 3 its last
+ * consumer warp finished its rows, 4 its last warp left; s = 5 is the SM id. Launches beyond `launches` are not
+ * traced; buffer = NULL switches tracing off (the default: the kernels then only test one pointer). Process-wide,
+ * host only. No counterpart in the reference. */
+#define DG_TRACE_CTAS 160
+#define DG_TRACE_SLOTS 8
+DG_API int dg_set_trace(void* buffer, int launches);
+
 /* Library version: 100 * major + minor. */
 DG_API int dg_version(void);
 

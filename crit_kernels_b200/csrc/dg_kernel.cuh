@@ -88,15 +88,34 @@ __host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class
 __host__ __device__ constexpr bool self_fed(int fmt, int m) {
   return shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && (fmt == FMT_BF16 || fmt == FMT_MXFP8));
 }
+// Class 2 by (format, M), measured on 28672 x 8192 (16384 x 8192 for BF16) over the candidates 8 warps x 4 rows,
+// 12 x 3, 12 x 4 and 16 x 2 (255, 168, 168 and 128 registers per thread): up to 14 % between them.
+__host__ __device__ constexpr int class2_warps(int fmt, int m) {
+  return fmt == FMT_FP8 ? (m <= 13 ? 12 : 8)
+         : fmt == FMT_BF16 ? (m <= 11 ? 12 : 8)
+         : fmt == FMT_NVFP4 ? (m == 8 ? 8 : m <= 11 ? 12 : 16) : 8;
+}
+__host__ __device__ constexpr int class2_rows(int fmt, int m) {
+  return fmt == FMT_NVFP4 ? (m == 5 || m == 8 ? 4 : m <= 11 ? 3 : 2) : 4;
+}
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
   return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12)
-         : shape_class(fmt, m) == 1 ? (self_fed(fmt, m) ? 12 : 11) : 8;
+         : shape_class(fmt, m) == 1 ? (self_fed(fmt, m) ? 12 : 11) : class2_warps(fmt, m);
 }
 __host__ __device__ constexpr int producer_warps(int fmt, int m) {
   return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : self_fed(fmt, m) ? 0 : 1;
 }
+// Kernels that advance their chains with the mixed-precision FMA instead of the packed FP32 FMA (same bits; see f2):
+// where the arithmetic is the limit, one issue slot per product without any conversion of the activations beats
+// half a slot per product plus the conversions. MXFP8 stays on the FP32 path: its weights carry their block scale,
+// and weight x 2^(e - 127) is not always a BF16 value.
+__host__ __device__ constexpr bool use_mixed(int fmt, int m) {
+  return fmt != FMT_MXFP8 && (shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && fmt != FMT_FP8));
+}
 // Rows a consumer warp holds at once (register budget).
-__host__ __device__ constexpr int rows_max(int fmt, int m) { return fmt == FMT_NVFP4 && m > 8 ? 3 : 4; }
+__host__ __device__ constexpr int rows_max(int fmt, int m) {
+  return shape_class(fmt, m) == 2 ? class2_rows(fmt, m) : 4;
+}
 
 struct Params {
   const void* x;             // [M][ldx] BF16 or FP16
@@ -184,6 +203,53 @@ __device__ __forceinline__ pk2 fmul2(pk2 a, pk2 b) {
   pk2 d;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
   return d;
+}
+
+// The same two chains as two plain FP32 registers, for the kernels that advance them with the mixed-precision FMA
+// (16-bit operands, FP32 addend and result, one rounding: fma.rn.f32.bf16 / fma.rn.f32.f16). The product of two 16-bit
+// operands is exact in FP32, so the result is bit for bit that of the FP32 FMA on the converted operands; what the
+// mixed form saves is the conversion of the activations to FP32, which it reads as loaded. There is no packed mixed
+// form, so these kernels issue one FMA per product.
+struct f2 { float lo, hi; };
+__device__ __forceinline__ float sum2(f2 a) { return a.lo + a.hi; }
+template <typename XT> struct Mixed;
+template <> struct Mixed<__nv_bfloat16> {
+  // (w.lo * x.lo + acc.lo, w.hi * x.hi + acc.hi): two BF16 pairs in 32-bit registers
+  __device__ __forceinline__ static f2 fma2(uint32_t w, uint32_t x, f2 acc) {
+    asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+        "mov.b32 {wl, wh}, %2;\n\tmov.b32 {xl, xh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, wl, xl, %0;\n\tfma.rn.f32.bf16 %1, wh, xh, %1;\n\t}"
+        : "+f"(acc.lo), "+f"(acc.hi) : "r"(w), "r"(x));
+    return acc;
+  }
+  // Two FP16 values that are exact in BF16 (decoded E4M3 / E2M1) as a BF16 pair: through FP32, every step exact.
+  __device__ __forceinline__ static uint32_t weights(uint32_t h) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&h));
+    const __nv_bfloat162 p = __floats2bfloat162_rn(t.x, t.y);
+    return *reinterpret_cast<const uint32_t*>(&p);
+  }
+};
+template <> struct Mixed<__half> {
+  __device__ __forceinline__ static f2 fma2(uint32_t w, uint32_t x, f2 acc) {
+    asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+        "mov.b32 {wl, wh}, %2;\n\tmov.b32 {xl, xh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, wl, xl, %0;\n\tfma.rn.f32.f16 %1, wh, xh, %1;\n\t}"
+        : "+f"(acc.lo), "+f"(acc.hi) : "r"(w), "r"(x));
+    return acc;
+  }
+  __device__ __forceinline__ static uint32_t weights(uint32_t h) { return h; }   // decoded weights are FP16 already
+};
+template <typename XT>
+__device__ __forceinline__ f2 mixed_fma4(const uint32_t (&w)[4], const uint4& x, f2 a) {
+  a = Mixed<XT>::fma2(w[0], x.x, a);
+  a = Mixed<XT>::fma2(w[1], x.y, a);
+  a = Mixed<XT>::fma2(w[2], x.z, a);
+  return Mixed<XT>::fma2(w[3], x.w, a);
+}
+template <typename XT, int R, int M>
+__device__ __forceinline__ void mixed_rows(const uint32_t (&w)[R][4], const uint4& x, f2 (&acc)[R][M], int m) {
+#pragma unroll
+  for (int r = 0; r < R; ++r) acc[r][m] = mixed_fma4<XT>(w[r], x, acc[r][m]);
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -676,6 +742,111 @@ __device__ __forceinline__ void body_nvfp4(uint32_t wrow, const uint32_t (&woff)
   }
 }
 
+// The same blocks with the mixed-precision FMA (use_mixed): the rows' weights are brought to the activations' 16-bit
+// type once per block (BF16 weights as stored; decoded E4M3 / E2M1 are FP16, exact in BF16 too) and held, the
+// activation rows stream past as loaded. Per (row, m): the operations and order of the bodies above.
+__device__ __forceinline__ void decode_e4m3_h(uint32_t a, uint32_t b, uint32_t (&h)[4]) {   // 8 E4M3 -> 4 FP16 pairs
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]) : "r"(a));
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+      : "=r"(h[2]), "=r"(h[3]) : "r"(b));
+}
+__device__ __forceinline__ void decode_e2m1_h(uint32_t a, uint32_t (&h)[4]) {               // 8 E2M1 -> 4 FP16 pairs
+  asm("{\n\t.reg .b8 c0, c1, c2, c3;\n\t"
+      "mov.b32 {c0, c1, c2, c3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, c0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, c1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, c2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, c3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(a));
+}
+
+template <int M, int R>
+__device__ __forceinline__ void body_bf16_mixed(uint32_t wrow, const uint32_t (&woff)[R], uint32_t xs, f2 (&acc)[R][M]) {
+  constexpr int XROW = 64 * Format<FMT_BF16>::E;
+  uint32_t w[R][4];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const uint4 v = lds128(wrow + woff[r]);
+    w[r][0] = v.x; w[r][1] = v.y; w[r][2] = v.z; w[r][3] = v.w;
+  }
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const uint4 xv = lds128(xs + m * XROW);
+    mixed_rows<__nv_bfloat16, R, M>(w, xv, acc, m);
+  }
+}
+
+template <int M, int R, typename XT>
+__device__ __forceinline__ void body_fp8_mixed(uint32_t wrow, const uint32_t (&woff)[R], uint32_t xs,
+                                               const XOffsets<2>& xo, f2 (&acc)[R][M]) {
+  constexpr int XROW = 64 * Format<FMT_FP8>::E;
+  uint4 wv[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) wv[r] = lds128(wrow + woff[r]);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    uint32_t w[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      decode_e4m3_h(j ? wv[r].z : wv[r].x, j ? wv[r].w : wv[r].y, w[r]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) w[r][q] = Mixed<XT>::weights(w[r][q]);
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint4 xv = lds128(xs + m * XROW + xo.off[j]);
+      mixed_rows<XT, R, M>(w, xv, acc, m);
+    }
+  }
+}
+
+// NVFP4: the partial sum of a scale block starts as a product; fma(a, b, -0) is that product bit for bit.
+template <int M, int R, typename XT>
+__device__ __forceinline__ void body_nvfp4_mixed(uint32_t wrow, const uint32_t (&woff)[R], const float2 (&sc)[R],
+                                                 uint32_t xs, const XOffsets<4>& xo, f2 (&acc)[R][M]) {
+  constexpr int XROW = 64 * Format<FMT_NVFP4>::E;
+  uint4 wv[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) wv[r] = lds128(wrow + woff[r]);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t wa[R][4], wb[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      decode_e2m1_h(h ? wv[r].z : wv[r].x, wa[r]);
+      decode_e2m1_h(h ? wv[r].w : wv[r].y, wb[r]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        wa[r][q] = Mixed<XT>::weights(wa[r][q]);
+        wb[r][q] = Mixed<XT>::weights(wb[r][q]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint4 xa = lds128(xs + m * XROW + xo.off[2 * h]);
+      const uint4 xb = lds128(xs + m * XROW + xo.off[2 * h + 1]);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        f2 part;
+        part.lo = -0.0f;
+        part.hi = -0.0f;
+        part = mixed_fma4<XT>(wa[r], xa, part);
+        part = mixed_fma4<XT>(wb[r], xb, part);
+        const float s = h ? sc[r].y : sc[r].x;
+        acc[r][m].lo = fmaf(s, part.lo, acc[r][m].lo);
+        acc[r][m].hi = fmaf(s, part.hi, acc[r][m].hi);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // Lane reduction of V values per lane at once: the xor-shuffle tree 16, 8, 4, 2, 1 of every value, with the values
 // split between the two partners at each level so that a level costs one shuffle per value pair instead of one per
@@ -733,6 +904,16 @@ __device__ __forceinline__ int lane_value(int lane, int slot) {
 // ---------------------------------------------------------------------------------------------------------------
 // One tile for one consumer warp holding up to R rows (nr of them real).
 
+template <bool MIXED> struct Chains;   // accumulator pair type of a kernel
+template <> struct Chains<false> {
+  using type = pk2;
+  __device__ __forceinline__ static pk2 zero() { return pack2(0.f, 0.f); }
+};
+template <> struct Chains<true> {
+  using type = f2;
+  __device__ __forceinline__ static f2 zero() { f2 z; z.lo = 0.f; z.hi = 0.f; return z; }
+};
+
 // SELF: the CTA has no producer warps; its consumer warps share the copies. A warp that has finished iteration `it`
 // (stage s) refills the stage of iteration it - 1, which every warp has probably left by then, with iteration
 // it + stages - 1: nobody waits for the slowest warp of the iteration just finished, and the ring runs one stage
@@ -755,13 +936,15 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
                                              int& it) {
   constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
   constexpr bool FEW = few_rows(FMT, M);
+  constexpr bool MIXED = use_mixed(FMT, M);
+  using Acc = typename Chains<MIXED>::type;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const XOffsets<NQ> xo(lane);
-  pk2 acc[R][M];
+  Acc acc[R][M];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = pack2(0.f, 0.f);
+    for (int m = 0; m < M; ++m) acc[r][m] = Chains<MIXED>::zero();
   // Offsets of the warp's rows inside a stage (rows are CW tile rows and one scale group apart); rows the warp does
   // not have alias its last real row (their sums are discarded).
   uint32_t woff[R], scoff[R];
@@ -787,10 +970,15 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
           const uint32_t wrow = stage + st * kStepBytes;
           const uint32_t xs = stage + lay.x_off + st * (M * 64 * E);
           if constexpr (FMT == FMT_BF16) {
-            body_bf16<FEW, M, R, XT>(wrow, woff, xs + lane * 16, acc);
+            if constexpr (MIXED) body_bf16_mixed<M, R>(wrow, woff, xs + lane * 16, acc);
+            else body_bf16<FEW, M, R, XT>(wrow, woff, xs + lane * 16, acc);
           } else if constexpr (FMT == FMT_FP8) {
-            float none[R];
-            body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, xo, acc);
+            if constexpr (MIXED) {
+              body_fp8_mixed<M, R, XT>(wrow, woff, xs, xo, acc);
+            } else {
+              float none[R];
+              body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, xo, acc);
+            }
           } else if constexpr (FMT == FMT_MXFP8) {
             float sc[R];
             if (staged) {
@@ -818,7 +1006,8 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
                 sc[r] = e4m3x2_to_f32(__ldg(reinterpret_cast<const uint16_t*>(p.scales + off)));
               }
             }
-            body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, xo, acc);
+            if constexpr (MIXED) body_nvfp4_mixed<M, R, XT>(wrow, woff, sc, xs, xo, acc);
+            else body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, xo, acc);
           }
         }
       }

@@ -1,28 +1,34 @@
 """Benchmark of the decode-GEMV hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|c1|stack]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--gather fused|fused-overlap|nccl]
 
 Metric: weight-stream throughput (algorithmic weight bytes / time, TB/s), the reference's headline for this path.
 
-Workloads
-  c1     (N = 1 default) FP8 E4M3 W8A16, K = 8192, N = 28672, a step = one call at each M in {1, 2, 4, 8, 16}, every
-         call on its own copy of the weights (5 x 235 MB in rotation, so nothing is served from the 126 MB L2). The
-         timed region replays a CUDA graph of the step (the reference's own method for its published numbers).
-  stack  (N > 1 default) the 70B-shaped NVFP4 projection stack: 80 layers x {qkv, o, gate_up, down}, output columns
-         sharded over the ranks, every GEMV with the all-gather of its [M][N/P] outputs in its epilogue (peer stores over
-         NVLink; `--gather nccl` runs an NCCL all-gather after every GEMV instead); a step = one pass
-         over the stack at each M in {1, 8, 16}, each pass one CUDA-graph replay. Total work is fixed ("strong").
+Workload (the same at every N, so that the 1 -> 8 GPU curve is one workload): the 70B-shaped NVFP4 projection stack,
+80 layers x {qkv 8192->10240, o 8192->8192, gate_up 8192->57344, down 28672->8192}, 38.5 GB of weights, output columns
+sharded over the N ranks. A step = one pass over the stack at each M in {1, 8, 16}; a pass is one CUDA-graph replay per
+rank; on N > 1 GPUs every GEMV ends with the all-gather of its outputs (fused into the kernel: peer stores over NVLink;
+`--gather nccl` runs an NCCL all-gather after every GEMV instead). Total work is fixed as N grows ("strong").
 
-The line printed by rank 0 carries: `value` (device-timed, inputs resident in HBM), `e2e` (the same step through the
-public torch ops with the activations copied from pinned host memory and the outputs copied back inside the timed
-region, uploads and downloads on their own streams beside the other calls of the step; the weights are the model and
-stay resident), `roofline` for the kernel that takes the most time with
-per-M detail, `cpu_baseline` (the reference tests' dequantize-then-matmul on the host cores, a bounded sample) and the
-SM clocks sampled while the GPU worked. `--impl reference` times that CPU path alone.
+The line rank 0 prints carries
+  value         device-timed (CUDA events, barrier + synchronize on both sides, max over ranks), inputs resident in HBM
+  e2e           the same step driven from host buffers: activations copied up from pinned memory and every role's
+                gathered output copied back inside the timed region
+  roofline      for the kernel with the largest share of the step (NVFP4, M = 16, gate_up), timed live; per_m = the
+                passes; per_config (N = 1) = the single-GPU configurations C0-C3 (NVFP4 4096^2, FP8 28672x8192, MXFP8
+                13824x5120, BF16 8192^2): median / min / max of 7 trials of graph replays over rotating weight copies,
+                against the HBM peak and the FP32-FMA ceiling, each checked against the CPU oracle on sampled rows, with
+                the reference's own sm_100a kernel timed beside it where that comparator was built (gpu_reference_us)
+  parity        after the timed region: N > 1: every rank recomputes the last layer's four projections from the whole
+                matrices on its own GPU and compares them bit for bit with what the sharded pass gathered; N = 1: the
+                same outputs against the CPU oracle on sampled rows, row i bit-identical across M, replays identical
+  cpu_baseline  (N = 1) the reference tests' dequantize-then-matmul on the host cores, on a bounded sample
+`--impl reference` times that CPU path alone on a bounded sample of the same workload (rank 0 only).
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -36,13 +42,17 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
-C1 = {"fmt": "fp8", "N": 28672, "K": 8192, "Ms": (1, 2, 4, 8, 16)}
 STACK_MS = (1, 8, 16)
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the c1 kernels, from the ncu captures summarised in
-# profiles/gemv_fp8_m1_28672x8192.md and profiles/gemv_fp8_m16_28672x8192.md (algorithmic bytes: 234,995,712).
-NCU_TRAFFIC_C1 = {1: 240_238_592, 16: 239_695_360}
 METRIC = "decode_gemv_weight_stream"
 UNIT = "TB/s"
+FMA_PER_CLK = 148 * 128
+# single-GPU configurations: id, format, N, K, row counts timed here (the tests sweep every M)
+CONFIGS = (("C0", "nvfp4", 4096, 4096, (1,)),
+           ("C1", "fp8", 28672, 8192, (1, 2, 4, 8, 16)),
+           ("C2", "mxfp8", 13824, 5120, (1, 4, 16)),
+           ("C3", "bf16", 8192, 8192, (1, 2, 4, 8, 16)))
+TRIALS = 7
+TRIAL_MS = 50.0
 
 
 def measured_peaks():
@@ -51,6 +61,17 @@ def measured_peaks():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def ncu_traffic(key):
+    """dram bytes per launch of a kernel from the tracked ncu summary (profiles/ncu_traffic.json), or None."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            entry = json.load(f).get(key)
+        return entry and entry.get("dram_bytes")
+    except OSError:
+        return None
 
 
 class ClockSampler:
@@ -122,203 +143,352 @@ def time_region(fn, reps, barrier=None):
     return a.elapsed_time(b)
 
 
+def trials_of(fn, per_call=1, barrier=None, reduce_max=None):
+    """Median / min / max over TRIALS trials of the device time of one fn(), each trial at least TRIAL_MS long.
+    per_call: GEMV calls inside one fn(). Returns microseconds per call."""
+    once = time_region(fn, 1, barrier)
+    reps = max(1, int(TRIAL_MS / max(once, 1e-3)) + 1)
+    times = []
+    for _ in range(TRIALS):
+        t = time_region(fn, reps, barrier) / reps
+        if reduce_max:
+            t = reduce_max(t)
+        times.append(t * 1e3 / per_call)
+    return {"us": statistics.median(times), "us_min": min(times), "us_max": max(times), "trials": TRIALS,
+            "ms_per_trial": reps * once}
+
+
+def graph_of(fn, dev):
+    """fn captured once in a CUDA graph (the calls allocate nothing and never wait for the device)."""
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def stack_config(world, layers, gather):
+    """The `config` both arms print for the same N."""
+    return {"workload": f"stack: NVFP4 W4A16, {layers} layers x (qkv 8192->10240, o 8192->8192, gate_up 8192->57344, "
+                        "down 28672->8192), one pass at each M in {1,8,16} per step",
+            "l2": "every projection has its own weights (38.5 GB in total; per GPU 38.5 GB / N >> the 126 MB L2)",
+            "parallelism": f"output columns sharded over {world} GPU(s)",
+            "gather": "none (1 GPU)" if world == 1 else gather}
+
+
 # ----- CPU arm: the reference tests' dequantize-then-matmul on the host cores -----------------------------------------
 
-def cpu_reference_sample(rows=2048, reps=1):
-    """One bounded sample of workload c1 on the host: `rows` output channels of the FP8 matrix, dequantised to FP32
-    and multiplied in FP32 at each M of the configuration. Returns (seconds per pass, weight bytes per pass)."""
+CPU_SAMPLE_DIV = 64     # the CPU arm multiplies 1 / 64 of every projection's output channels of one layer
+
+
+def cpu_stack_sample(reps=1):
+    """One bounded sample of the stack workload on the host: for each of a layer's four projections, N / 64 output
+    channels of an NVFP4 matrix in the workload's distribution, dequantised to FP32 and multiplied in FP32 at each M
+    in {1, 8, 16} (the dequantisation is part of every call, as in the reference's dequantize-then-matmul path).
+    Returns (seconds per step of the sample, weight bytes the sample streams per step, description)."""
     from oracle import decode_gemv_oracle as oc
     from oracle import workloads as wl
-    codes, scale = wl.cfg_fp8(rows, C1["K"], seed=1)
-    xs = [wl.activations(m, C1["K"], seed=8) for m in C1["Ms"]]
+    mats = [(wl.cfg_nvfp4(n // CPU_SAMPLE_DIV, k, seed=70 + i), k) for i, (_, k, n) in enumerate(wl.STACK_ROLES)]
+    xs = {(m, k): wl.activations(m, k, seed=8 + m) for m in STACK_MS for _, k in mats}
     best = None
     for _ in range(reps):
         t0 = time.perf_counter()
-        for x in xs:
-            oc.gemv_fp32(x, oc.dequant_fp32("fp8", (codes, scale)))
+        for m in STACK_MS:
+            for tensors, k in mats:
+                oc.gemv_fp32(xs[(m, k)], oc.dequant_fp32("nvfp4", tensors))
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return best, len(C1["Ms"]) * wl.weight_bytes("fp8", rows, C1["K"])
+    nbytes = len(STACK_MS) * sum(wl.weight_bytes("nvfp4", n // CPU_SAMPLE_DIV, k) for _, k, n in wl.STACK_ROLES)
+    what = (f"1/{CPU_SAMPLE_DIV} of the output channels of each of one layer's four projections at each M in "
+            f"{list(STACK_MS)}: FP32 dequantise + FP32 matmul with torch on the host")
+    return best, nbytes, what
 
 
 def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    rows = 2048
+    torch.set_num_threads(os.cpu_count() or 1)     # torch.distributed.run exports OMP_NUM_THREADS=1
     for _ in range(max(args.warmup, 1)):
-        cpu_reference_sample(rows)
+        cpu_stack_sample()
     times = []
     for _ in range(args.steps):
-        dt, nbytes = cpu_reference_sample(rows)
+        dt, nbytes, what = cpu_stack_sample()
         times.append(dt)
     sec = sum(times) / len(times)
     value = nbytes / sec / 1e12
-    cores = torch.get_num_threads()
-    sample = f"{rows} of {C1['N']} output channels of workload c1, M in {list(C1['Ms'])}, torch CPU FP32"
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "c1: FP8 E4M3 W8A16 GEMV K=8192 N=28672 M in {1,2,4,8,16} (CPU arm: bounded sample)"},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": stack_config(args.gpus, args.layers or 80, args.gather),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": what},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-# ----- workload c1 on one GPU --------------------------------------------------------------------------------------
+# ----- the stack on N GPUs ---------------------------------------------------------------------------------------------
 
-def run_c1(args, dev):
-    import crit_kernels_b200
-    from oracle import workloads as wl
-    from crit_kernels_b200 import cabi
-    k = crit_kernels_b200.get_kernel("crit-labs/decode-gemv", version=1)
-    cabi.load().dg_set_static_weights(1)     # the weights are resident and never rewritten between calls
-    n, kk, ms = C1["N"], C1["K"], C1["Ms"]
-    g = torch.Generator(device=dev).manual_seed(1234)
-    copies = []
-    for _ in range(len(ms)):
-        codes = (torch.randn(n, kk, device=dev, generator=g) * 0.02).to(torch.float8_e4m3fn).view(torch.uint8)
-        scale = (torch.rand(n, device=dev, generator=g) * 1.5 + 0.5) / 64
-        copies.append((codes, scale))
-    xs_host = [wl.activations(m, kk, seed=8 + m).pin_memory() for m in ms]
-    xs = [x.to(dev) for x in xs_host]
-    outs = [torch.empty(m, n, dtype=torch.bfloat16, device=dev) for m in ms]
-    outs_host = [torch.empty(m, n, dtype=torch.bfloat16).pin_memory() for m in ms]
-    wbytes = wl.weight_bytes("fp8", n, kk)
-
-    def step():
-        for i in range(len(ms)):
-            k.gemv_fp8(xs[i], copies[i][0], copies[i][1], outs[i])
-
-    up, down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    # a small call first and last: the largest upload and the largest download then run beside other calls
-    e2e_order = sorted(range(len(ms)), key=lambda i: (ms[i] == min(ms), -ms[i]))
-    e2e_order = e2e_order[-2:-1] + e2e_order[:-2] + e2e_order[-1:] if len(ms) > 2 else e2e_order
-
-    def step_e2e_body():
-        # what a serving loop does per decode step: activations up from pinned host memory, the GEMV through the
-        # public op, results down to pinned host memory (the weights are the model and stay resident). Uploads and
-        # downloads run on their own streams, each call waits for its own activations only and each download for
-        # its own call only; the step ends when every download has landed.
-        main = torch.cuda.current_stream()
-        up.wait_stream(main)
-        down.wait_stream(main)
-        ready = []
-        with torch.cuda.stream(up):
-            for i in e2e_order:
-                xs[i].copy_(xs_host[i], non_blocking=True)
-                ready.append(torch.cuda.Event())
-                ready[-1].record(up)
-        for j, i in enumerate(e2e_order):
-            main.wait_event(ready[j])
-            k.gemv_fp8(xs[i], copies[i][0], copies[i][1], outs[i])
-            done = torch.cuda.Event()
-            done.record(main)
-            down.wait_event(done)
-            with torch.cuda.stream(down):
-                outs_host[i].copy_(outs[i], non_blocking=True)
-        main.wait_stream(up)
-        main.wait_stream(down)
-
-    def graph_of(fn):
-        """fn captured once in a CUDA graph (the calls allocate nothing and never wait for the device)."""
-        side = torch.cuda.Stream(device=dev)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            fn()
-        torch.cuda.current_stream().wait_stream(side)
+def stack_parity(model, runs, dev, rank, world):
+    """Untimed gate after the timed region (see the module docstring). Returns the `parity` object; raises on a
+    mismatch."""
+    from crit_kernels_b200 import stack as stk
+    from oracle import decode_gemv_oracle as oc
+    roles = model.roles
+    layer = model.layers - 1
+    checked, oracle_rows = 0, 0
+    first_rows = {}
+    for m in STACK_MS:
+        run = runs[m]
+        run.replay()
         torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn()
-        return g
-
-    with ClockSampler(dev.index or 0) as clocks:
-        step_graph = graph_of(step)
-        for _ in range(args.warmup):
-            step_graph.replay()
-        ms_total = time_region(step_graph.replay, args.steps)
-        # per-M kernel times: a graph of ten calls at that M, rotating over the weight copies
-        per_m = []
-        for i, m in enumerate(ms):
-            def ten(i=i):
-                for c in range(10):
-                    w = copies[c % len(copies)]
-                    k.gemv_fp8(xs[i], w[0], w[1], outs[i])
-            g = graph_of(ten)
-            for _ in range(3):
-                g.replay()
-            reps = max(5, args.steps // 10)
-            per_m.append(time_region(g.replay, reps) / (10 * reps))
-        e2e_graph = graph_of(step_e2e_body)      # the copies are captured with the calls: one replay + one wait per step
-        for _ in range(3):
-            e2e_graph.replay()
-            torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            e2e_graph.replay()
-            torch.cuda.synchronize()             # the host reads the results every step
-        e2e_s = (time.perf_counter() - t0) / args.steps
-        for i in range(len(ms)):                 # what came down is what the calls wrote
-            if not torch.equal(outs_host[i], outs[i].cpu()):
-                raise RuntimeError(f"end-to-end step: downloaded results of M={ms[i]} differ from the device's")
-    return {"ms_per_step": ms_total / args.steps, "bytes_per_step": wbytes * len(ms), "per_m_ms": per_m,
-            "wbytes": wbytes, "clocks": clocks.summary(), "e2e_s": e2e_s,
-            "h2d": sum(x.numel() * 2 for x in xs_host), "d2h": sum(o.numel() * 2 for o in outs_host),
-            "launches": args.steps * len(ms)}
+        got = {role: t.clone() for role, t in run.outputs().items()}
+        run.replay()
+        torch.cuda.synchronize()
+        for role, t in run.outputs().items():
+            if not torch.equal(t.view(torch.int16), got[role].view(torch.int16)):
+                raise RuntimeError(f"parity: M={m} {role}: two replays differ")
+        for idx, (role, k, n) in enumerate(roles):
+            codes, scales, inverse = stk.ShardedStack.full_matrix(model.seed, layer, idx, roles[idx], dev)
+            if world > 1:
+                want = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+                model.kernel.gemv(run.x[role], codes, scales, inverse, want)
+                torch.cuda.synchronize()
+                if not torch.equal(want.view(torch.int16), got[role].view(torch.int16)):
+                    raise RuntimeError(f"parity: M={m} {role}: the gathered output differs from the single-GPU output")
+            else:
+                rows = torch.arange(0, n, max(1, n // 48))[:48]
+                sub = (codes[rows].cpu(), scales[rows].cpu(), inverse[rows].cpu())
+                exact = oc.gemv_exact(run.x[role].cpu(), oc.values_of("nvfp4", sub))
+                err = oc.max_rel_error(got[role][:, rows].cpu(), exact)
+                if not err <= 1e-2:
+                    raise RuntimeError(f"parity: M={m} {role}: max relative error {err} against the oracle")
+                oracle_rows += len(rows)
+            row0 = got[role][0].view(torch.int16)
+            if role in first_rows and not torch.equal(first_rows[role], row0):
+                raise RuntimeError(f"parity: {role}: row 0 differs between M={m} and M={STACK_MS[0]}")
+            first_rows.setdefault(role, row0)
+            checked += 1
+            del codes, scales, inverse
+    out = {"checked": True, "ranks": world, "projections": checked, "bit_equal": True,
+           "row_invariant_across_m": True, "replays_identical": True}
+    if world == 1:
+        out["oracle_rows"] = oracle_rows
+        out["oracle_tolerance"] = "max relative error <= 1e-2 of the FP64 product, BF16 outputs"
+    else:
+        out["against"] = "the whole matrices multiplied on each rank's own GPU (last layer, 4 projections x 3 M)"
+    return out
 
 
-# ----- workload stack on N GPUs ------------------------------------------------------------------------------------
-
-def run_stack(args, dev, rank, world, ms=STACK_MS, layers=None):
+def run_stack(args, dev, rank, world):
     import torch.distributed as dist
-    import crit_kernels_b200
+    from crit_kernels_b200 import cabi
     from crit_kernels_b200 import stack as stk
     from oracle import workloads as wl
-    layers = layers or wl.STACK_LAYERS
+    layers = args.layers or wl.STACK_LAYERS
     model = stk.ShardedStack.random(layers, wl.STACK_ROLES, rank, world, dev, seed=99, gather=args.gather)
-    runs = {m: model.capture(m) for m in ms}
+    runs = {m: model.capture(m) for m in STACK_MS}
     barrier = (lambda: dist.barrier()) if world > 1 else None
 
+    def reduce_max(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     def step():
-        for m in ms:
+        for m in STACK_MS:
             runs[m].replay()
 
     with ClockSampler(dev.index or 0) as clocks:
         for _ in range(args.warmup):
             step()
-        ms_total = time_region(step, args.steps, barrier)
-        per_m = []
-        for m in ms:
-            reps = max(3, args.steps)
-            per_m.append(time_region(runs[m].replay, reps, barrier) / reps)
-        # end to end: activations from pinned host memory, the last projection's gathered output back
+        ms_step = reduce_max(time_region(step, args.steps, barrier) / args.steps)
+        per_m = [trials_of(runs[m].replay, 1, barrier, reduce_max) for m in STACK_MS]
+        # the kernel with the largest share: NVFP4 M = 16 on gate_up (with its all-gather on N > 1), timed alone over
+        # the layers' distinct weights
+        m_top = STACK_MS[-1]
+        top = runs[m_top]
+        gate = [p for p in model.projections if p.role == "gate_up"]
+
+        def gate_ups():
+            for p in gate[:16]:
+                if top.fused:
+                    top._gemv_allgather(p)
+                else:
+                    model.kernel.gemv(top.x[p.role], p.codes, p.scales, p.inverse, top.shard[p.role])
+        cabi.load().dg_set_static_weights(1)
+        g_top = graph_of(gate_ups, dev)
+        cabi.load().dg_set_static_weights(0)
+        top_kernel = trials_of(g_top.replay, min(16, len(gate)), barrier, reduce_max)
+        del g_top
+        # end to end: activations from pinned host memory, every role's gathered output back
         for _ in range(2):
-            for m in ms:
+            for m in STACK_MS:
                 runs[m].replay_e2e()
         if barrier:
             barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            for m in ms:
+            for m in STACK_MS:
                 runs[m].replay_e2e()
         torch.cuda.synchronize()
-        e2e_s = (time.perf_counter() - t0) / args.steps
-    t = torch.tensor([ms_total / args.steps, e2e_s * 1e3] + per_m, dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    t = t.tolist()
+        e2e_s = reduce_max((time.perf_counter() - t0) / args.steps)
+    parity = stack_parity(model, runs, dev, rank, world)
     full_bytes = layers * sum(wl.weight_bytes("nvfp4", n, k) for _, k, n in wl.STACK_ROLES)
-    return {"ms_per_step": t[0], "e2e_s": t[1] / 1e3, "per_m_ms": t[2:], "bytes_per_step": full_bytes * len(ms),
-            "pass_bytes": full_bytes, "clocks": clocks.summary(),
-            "h2d": sum(runs[m].h2d_bytes for m in ms), "d2h": sum(runs[m].d2h_bytes for m in ms),
-            "launches": args.steps * sum(runs[m].kernel_launches for m in ms), "gather": model.gather_kind}
+    gate_bytes = wl.weight_bytes("nvfp4", 57344 // world, 8192)
+    return {"ms_per_step": ms_step, "e2e_s": e2e_s, "per_m": per_m, "bytes_per_step": full_bytes * len(STACK_MS),
+            "pass_bytes": full_bytes, "clocks": clocks.summary(), "top_kernel": top_kernel, "top_bytes": gate_bytes,
+            "h2d": sum(runs[m].h2d_bytes for m in STACK_MS), "d2h": sum(runs[m].d2h_bytes for m in STACK_MS),
+            "launches": args.steps * sum(runs[m].kernel_launches for m in STACK_MS), "gather": model.gather_kind,
+            "parity": parity, "layers": layers, "model": model, "runs": runs}
+
+
+# ----- single-GPU configurations C0-C3 -----------------------------------------------------------------------------
+
+def make_copies(fmt, n, k, dev, copies):
+    """`copies` matrices of one configuration in its benchmark distribution, generated on the device."""
+    g = torch.Generator(device=dev).manual_seed(4321)
+    out = []
+    for _ in range(copies):
+        if fmt == "nvfp4":
+            c = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=g)
+            s = torch.exp2(torch.rand(n, k // 16, device=dev, generator=g) * 6 - 4).to(torch.float8_e4m3fn)
+            out.append((c, s.view(torch.uint8), torch.ones(n, device=dev)))
+        elif fmt == "fp8":
+            c = (torch.randn(n, k, device=dev, generator=g) * 0.02).to(torch.float8_e4m3fn).view(torch.uint8)
+            out.append((c, (torch.rand(n, device=dev, generator=g) * 1.5 + 0.5) / 64))
+        elif fmt == "mxfp8":
+            w = (torch.randn(n, k, device=dev, generator=g) * 0.02).view(n, k // 32, 32)
+            _, e = torch.frexp(w.abs().amax(dim=-1))
+            shared = torch.where(w.abs().amax(dim=-1) > 0, e - 1 - 8, torch.zeros_like(e)).clamp(-127, 127).float()
+            c = (w / torch.exp2(shared)[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+            out.append((c.view(n, k), (shared + 127).to(torch.uint8)))
+        else:
+            out.append(((torch.randn(n, k, device=dev, generator=g) * 0.02).to(torch.bfloat16),))
+    return out
+
+
+def run_configs(dev, hbm_gbs, sm_mhz):
+    """C0-C3 on one GPU: per (configuration, M) the time of a call (graph replays over rotating weight copies larger
+    than L2 in total), the same for the reference's sm_100a kernel when oracle/_ref holds it, and an oracle check."""
+    import crit_kernels_b200
+    from oracle import build_ref
+    from oracle import decode_gemv_oracle as oc
+    from oracle import workloads as wl
+    k_mod = crit_kernels_b200.get_kernel("crit-labs/decode-gemv", version=1)
+    ref = build_ref.load()
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    entries = []
+    for cid, fmt, n, k, ms in CONFIGS:
+        nbytes = wl.weight_bytes(fmt, n, k)
+        copies = max(2, min(32, int(1.0e9 // nbytes)))          # >= 256 MB of distinct weights in rotation
+        while copies * nbytes < 256e6:
+            copies += 1
+        ws = make_copies(fmt, n, k, dev, copies)
+        x16 = wl.activations(16, k, seed=8).to(dev)
+        calls = max(copies, 8)
+        rows = torch.arange(0, n, max(1, n // 64))[:64]
+        values = oc.values_of(fmt, tuple(t[rows].cpu() if t.dim() and t.shape[0] == n else t.cpu() for t in ws[0]))
+        row0 = None
+        for m in ms:
+            x = x16[:m].contiguous()
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+
+            def ours(i):
+                t = ws[i % copies]
+                if fmt == "nvfp4":
+                    k_mod.gemv(x, t[0], t[1], t[2], out)
+                elif fmt == "bf16":
+                    k_mod.gemv_bf16(x, t[0], out)
+                else:
+                    k_mod.gemv_fp8(x, t[0], t[1], out)
+
+            def theirs(i):
+                t = ws[i % copies]
+                st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+                if fmt == "nvfp4":
+                    rc = ref.ref_enqueue_nvfp4(ptr(x), x.stride(0), 1, ptr(t[0]), ptr(t[1]), 0, ptr(t[2]), ptr(out),
+                                               out.stride(0), 1, m, n, k, st)
+                elif fmt == "bf16":
+                    rc = ref.ref_enqueue_bf16(ptr(x), x.stride(0), ptr(t[0]), ptr(out), out.stride(0), 1, m, n, k, st)
+                else:
+                    mx = fmt == "mxfp8"
+                    rc = ref.ref_enqueue_fp8(ptr(x), x.stride(0), 1, ptr(t[0]), None if mx else ptr(t[1]),
+                                             ptr(t[1]) if mx else None, ptr(out), out.stride(0), 1, m, n, k, st)
+                if rc:
+                    raise RuntimeError(f"reference kernel refused {cid} M={m}: cudaError {rc}")
+
+            def many(fn):
+                return lambda: [fn(i) for i in range(calls)]
+            # oracle check and invariants on copy 0
+            ours(0)
+            torch.cuda.synchronize()
+            first = out.clone()
+            err = oc.max_rel_error(first[:, rows].cpu(), oc.gemv_exact(x.cpu(), values))
+            if not err <= 1e-2:
+                raise RuntimeError(f"{cid} M={m}: max relative error {err} against the oracle")
+            ours(0)
+            torch.cuda.synchronize()
+            if not torch.equal(out.view(torch.int16), first.view(torch.int16)):
+                raise RuntimeError(f"{cid} M={m}: two calls differ")
+            if row0 is not None and not torch.equal(row0, first[0].view(torch.int16)):
+                raise RuntimeError(f"{cid}: row 0 differs between M={m} and M={ms[0]}")
+            row0 = first[0].view(torch.int16).clone()
+            g = graph_of(many(ours), dev)
+            t_ours = trials_of(g.replay, calls)
+            del g
+            entry = {"config": cid, "fmt": fmt, "N": n, "K": k, "M": m, "us": t_ours["us"], "us_min": t_ours["us_min"],
+                     "us_max": t_ours["us_max"], "trials": TRIALS, "ms_per_trial": t_ours["ms_per_trial"],
+                     "weight_bytes": nbytes, "copies_in_rotation": copies,
+                     "GBps": nbytes / t_ours["us"] / 1e3, "frac_hbm": nbytes / t_ours["us"] / 1e3 / hbm_gbs,
+                     "frac_fp32_fma": m * n * k / (t_ours["us"] * 1e-6) / (FMA_PER_CLK * sm_mhz * 1e6),
+                     "oracle_max_rel_err": err, "gpu_reference_us": None, "speedup_vs_gpu_reference": None}
+            if ref is not None:
+                g = graph_of(many(theirs), dev)
+                t_ref = trials_of(g.replay, calls)
+                del g
+                entry["gpu_reference_us"] = t_ref["us"]
+                entry["gpu_reference_us_minmax"] = [t_ref["us_min"], t_ref["us_max"]]
+                entry["speedup_vs_gpu_reference"] = t_ref["us"] / t_ours["us"]
+            entries.append(entry)
+        del ws
+        torch.cuda.empty_cache()
+    return entries
+
+
+def host_cost(dev):
+    """Host time of one eager (un-captured) call through the public op: what a caller that does not use CUDA graphs
+    pays per GEMV. 1000 calls of a small NVFP4 GEMV, wall clock around the enqueues only."""
+    import crit_kernels_b200
+    from oracle import workloads as wl
+    k_mod = crit_kernels_b200.get_kernel("crit-labs/decode-gemv", version=1)
+    n, k = 1024, 4096
+    c, s, i = (t.to(dev) for t in wl.cfg_nvfp4(n, k))
+    x = wl.activations(1, k).to(dev)
+    out = torch.empty(1, n, dtype=torch.bfloat16, device=dev)
+    for _ in range(50):
+        k_mod.gemv(x, c, s, i, out)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(1000):
+        k_mod.gemv(x, c, s, i, out)
+    dt = time.perf_counter() - t0
+    torch.cuda.synchronize()
+    return dt / 1000 * 1e6
 
 
 def run_case(args):
-    """`--case fmt:M:N:K`: seeded inputs in the benchmark distributions, --warmup + --steps calls, device time."""
+    """`--case fmt:M:N:K`: seeded inputs in the benchmark distributions, --warmup + --steps calls, device time: the
+    small program that profilers capture."""
     import crit_kernels_b200
     from oracle import workloads as wl
     fmt, m, n, kk = args.case.split(":")
@@ -360,21 +530,22 @@ def leave_distributed():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "c1", "stack"])
     ap.add_argument("--layers", type=int, default=None, help="stack depth (default 80)")
     ap.add_argument("--gather", default="fused", choices=["fused", "fused-overlap", "nccl"],
-                    help="stack workload on N > 1 GPUs: all-gather fused into the GEMV epilogue, or NCCL per GEMV")
+                    help="N > 1 GPUs: all-gather fused into the GEMV epilogue (default), the same with the arrivals "
+                         "collected once per pass (legal only because the stack's GEMVs are independent), or NCCL")
+    ap.add_argument("--no-configs", action="store_true", help="skip the single-GPU configurations C0-C3")
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
                     help="run `--steps` calls of one GEMV (fmt in bf16, fp8, mxfp8, nvfp4) and exit: the small case "
                          "profilers capture")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
         return
+    args.warmup = max(args.warmup, 3)
     if args.case:
         run_case(args)
         return
@@ -386,65 +557,62 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    workload = args.workload if args.workload != "auto" else ("c1" if world == 1 else "stack")
     hbm_gbs, peak_kind = measured_peaks()
-    fma_per_clk = 148 * 128
 
-    if workload == "c1":
-        r = run_c1(args, dev)
-        ms, n, kk = C1["Ms"], C1["N"], C1["K"]
-        sm_mhz = r["clocks"]["sm_mhz"] or 1965.0
-        detail = []
-        for m, t_ms in zip(ms, r["per_m_ms"]):
-            gbs = r["wbytes"] / (t_ms * 1e-3) / 1e9
-            fma_rate = m * n * kk / (t_ms * 1e-3)
-            detail.append({"M": m, "us": t_ms * 1e3, "GBps": gbs, "frac_hbm": gbs / hbm_gbs,
-                           "frac_fp32_fma": fma_rate / (fma_per_clk * sm_mhz * 1e6)})
-        top = max(range(len(ms)), key=lambda i: r["per_m_ms"][i])
-        roofline = {"bound": "hbm", "kernel": f"gemv_kernel<FP8, M={ms[top]}, bf16>",
-                    "achieved": detail[top]["GBps"], "peak": hbm_gbs, "unit": "GB/s",
-                    "frac": detail[top]["frac_hbm"], "traffic": NCU_TRAFFIC_C1.get(ms[top]), "peak_kind": peak_kind,
-                    "frac_fp32_fma_ceiling": detail[top]["frac_fp32_fma"], "per_m": detail}
-        config = {"workload": "c1: FP8 E4M3 W8A16 GEMV K=8192 N=28672, one call at each M in {1,2,4,8,16} per step",
-                  "l2": "each call streams its own 235 MB copy of the weights (5 copies in rotation, 126 MB L2)",
-                  "parallelism": "1 GPU", "launch": "CUDA graph of the step; programmatic dependent launch with static "
-                                                    "weights (dg_set_static_weights(1))"}
-        scaling = "weak"
-    else:
-        r = run_stack(args, dev, rank, world, layers=args.layers)
-        detail = []
-        for m, t_ms in zip(STACK_MS, r["per_m_ms"]):
-            gbs = r["pass_bytes"] / (t_ms * 1e-3) / 1e9
-            detail.append({"M": m, "ms_per_pass": t_ms, "GBps_all_gpus": gbs, "frac_hbm": gbs / (hbm_gbs * world)})
-        top = max(range(len(STACK_MS)), key=lambda i: r["per_m_ms"][i])
-        roofline = {"bound": "hbm", "kernel": f"gemv_kernel<NVFP4, M={STACK_MS[top]}, bf16> (+ all-gather)",
-                    "achieved": detail[top]["GBps_all_gpus"] / world, "peak": hbm_gbs, "unit": "GB/s",
-                    "frac": detail[top]["frac_hbm"], "traffic": None, "peak_kind": peak_kind, "per_m": detail}
-        config = {"workload": f"stack: NVFP4 W4A16, {args.layers or 80} layers x (qkv 8192->10240, o 8192->8192, "
-                              "gate_up 8192->57344, down 28672->8192), one pass at each M in {1,8,16} per step",
-                  "l2": f"every projection has its own weights ({r['pass_bytes'] / world / 1e9:.1f} GB per GPU)",
-                  "parallelism": f"output columns sharded over {world} GPU(s); gather: {r['gather']}"}
-        scaling = "strong"
-
+    r = run_stack(args, dev, rank, world)
+    sm_mhz = r["clocks"]["sm_mhz"] or 1965.0
+    detail = []
+    for m, t in zip(STACK_MS, r["per_m"]):
+        gbs = r["pass_bytes"] / (t["us"] * 1e-6) / 1e9
+        detail.append({"M": m, "ms_per_pass": t["us"] / 1e3, "ms_min": t["us_min"] / 1e3, "ms_max": t["us_max"] / 1e3,
+                       "trials": TRIALS, "GBps_all_gpus": gbs, "frac_hbm": gbs / (hbm_gbs * world)})
+    top_us = r["top_kernel"]["us"]
+    top_gbs = r["top_bytes"] / top_us / 1e3
+    n_top = 57344 // world
+    roofline = {"bound": "hbm", "kernel": f"gemv_kernel<NVFP4, M=16, bf16> on gate_up {n_top} x 8192"
+                                          + (" with its all-gather" if world > 1 else ""),
+                "achieved": top_gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": top_gbs / hbm_gbs,
+                "traffic": ncu_traffic(f"nvfp4:16:{n_top}:8192"), "peak_kind": peak_kind,
+                "us": top_us, "us_minmax": [r["top_kernel"]["us_min"], r["top_kernel"]["us_max"]],
+                "algorithmic_bytes": r["top_bytes"],
+                "frac_fp32_fma_ceiling": 16 * n_top * 8192 / (top_us * 1e-6) / (FMA_PER_CLK * sm_mhz * 1e6),
+                "note": "M = 16 on CUDA cores is bound by FP32 FMA issue, not HBM (16 FMAs per 4-bit weight): the FMA "
+                        "floor of this call is 16 N K / (148 x 128 x clock)",
+                "per_m": detail}
+    model, runs = r.pop("model"), r.pop("runs")
+    per_config, host_us = None, None
+    if world == 1:
+        runs.clear()
+        del model
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        host_us = host_cost(dev)
+        if not args.no_configs:
+            per_config = run_configs(dev, hbm_gbs, sm_mhz)
+            roofline["per_config"] = per_config
     if rank != 0:
         if world > 1:
+            runs.clear()
             leave_distributed()
         return
     value = r["bytes_per_step"] / (r["ms_per_step"] * 1e-3) / 1e12
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": scaling,
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "clocks": r["clocks"],
+            "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": stack_config(world, r["layers"], args.gather), "clocks": r["clocks"],
             "e2e": {"value": r["bytes_per_step"] / r["e2e_s"] / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
-            "gpu_launches": r["launches"], "roofline": roofline}
+            "gpu_launches": r["launches"], "roofline": roofline, "parity": r["parity"], "gather": r["gather"]}
+    if host_us is not None:
+        line["host_us_per_eager_call"] = host_us
     if world == 1:
-        sec, nbytes = cpu_reference_sample(2048, reps=3)
+        sec, nbytes, what = cpu_stack_sample(reps=2)
         line["cpu_baseline"] = {"value": nbytes / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
-                                "kind": "port",
-                                "sample": "2048 of 28672 output channels of workload c1 at each M in {1,2,4,8,16}: "
-                                          "FP32 dequantise + FP32 matmul with torch on the host"}
+                                "kind": "port", "sample": what}
     print(json.dumps(line), flush=True)
     if world > 1:
+        runs.clear()
         leave_distributed()
 
 

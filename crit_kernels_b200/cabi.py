@@ -24,6 +24,9 @@ SIGNATURES = {
     "dg_take_status": (_i, []),
     "dg_set_static_weights": (_i, [_i]),
     "dg_set_trace": (_i, [_p, _i]),
+    "dg_reset_counters": (_i, [_p, _p]),
+    "dg_reset_noalloc_channel": (_i, [_i, _p]),
+    "dg_set_wait_limit_ns": (ctypes.c_ulonglong, [ctypes.c_ulonglong]),
     "dg_version": (_i, []),
 }
 FMT = {"bf16": 0, "fp8": 1, "mxfp8": 2, "nvfp4": 3}

@@ -59,6 +59,7 @@ bool encode_rows(CUtensorMap* map, const void* base, int rows, int row_bytes, in
 }
 DeviceState g_devices[kMaxDevices];
 std::atomic<int> g_static_weights{0};   // dg_set_static_weights
+std::atomic<unsigned long long> g_wait_limit_ns{dg::kWaitLimitNs};   // dg_set_wait_limit_ns
 // dg_set_trace: launch i of the GEMV kernels (counted from the call that set the buffer) stamps into region i
 std::atomic<unsigned long long*> g_trace_base{nullptr};
 std::atomic<int> g_trace_capacity{0}, g_trace_next{0};
@@ -161,6 +162,9 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   if (p.use_2d && p.scale_mode == dg::SCALES_STAGED)
     p.use_2d = encode_rows(&p.tmap_sc, p.scales, p.N, p.scale_row_bytes, cw, p.steps * kFormats[fmt].scb);
   p.early_weights = g_static_weights.load(std::memory_order_relaxed);
+  p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  static const bool no_split = std::getenv("DG_NO_SPLIT_TAIL") != nullptr;   // tuning aid
+  p.split_tail = M == 1 && !no_split;
   if (unsigned long long* base = g_trace_base.load(std::memory_order_acquire)) {
     const int index = g_trace_next.fetch_add(1, std::memory_order_relaxed);
     if (index < g_trace_capacity.load(std::memory_order_relaxed))
@@ -236,14 +240,15 @@ int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint
 }
 
 // Waits (bounded) until counter `slot` of this rank's block holds `expected` arrivals, then takes them off.
-__global__ void gather_wait_kernel(unsigned int* counter, unsigned int expected, int* status) {
+__global__ void gather_wait_kernel(unsigned int* counter, unsigned int expected, int* status,
+                                   unsigned long long limit_ns) {
   const unsigned long long start = dg::global_ns();
   bool done = false;
   for (unsigned int i = 1; !done; ++i) {
     unsigned int seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
     done = seen >= expected;
-    if (!done && (i & 63u) == 0u && dg::global_ns() - start > dg::kWaitLimitNs) break;
+    if (!done && (i & 63u) == 0u && dg::global_ns() - start > limit_ns) break;
   }
   if (done) atomicSub_system(counter, expected);
   else if (status) atomicOr(status, dg::kStatusGatherTimeout);
@@ -255,8 +260,14 @@ int dg_enqueue_gather_wait(void* flags, int slot, unsigned int expected, void* s
   if (!st) return (int)cudaErrorInvalidDevice;
   if (!flags || !aligned(flags, 4) || (slot != 0 && slot != 1) || expected == 0) return (int)cudaErrorInvalidValue;
   gather_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned int*>(flags) + slot, expected,
-                                                                    st->status);
+                                                                    st->status,
+                                                                    g_wait_limit_ns.load(std::memory_order_relaxed));
   return (int)cudaGetLastError();
+}
+
+int dg_reset_counters(void* flags, void* stream) {
+  if (!flags || !aligned(flags, 4)) return (int)cudaErrorInvalidValue;
+  return (int)cudaMemsetAsync(flags, 0, 4 * sizeof(unsigned int), static_cast<cudaStream_t>(stream));
 }
 
 // ---- the entry point that allocates nothing ---------------------------------------------------------------------
@@ -266,11 +277,11 @@ int dg_enqueue_gather_wait(void* flags, int slot, unsigned int expected, void* s
 // handle for the runtime, not a device address: the address a kernel may use comes from cudaGetSymbolAddress, asked
 // once per device with that device current.
 static __device__ __align__(256) unsigned int dg_gather_scratch[4 * DG_NOALLOC_CHANNELS];
-static unsigned int* g_gather_scratch[kMaxDevices];   // per device, filled by the first call that names the device
+static std::atomic<unsigned int*> g_gather_scratch[kMaxDevices];   // per device, filled by the first call that names it
 
 static cudaError_t gather_scratch_of(int device, unsigned int** out) {
   if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
-  if (!g_gather_scratch[device]) {
+  if (!g_gather_scratch[device].load(std::memory_order_acquire)) {
     int previous = 0;
     cudaError_t e = cudaGetDevice(&previous);
     if (e == cudaSuccess && previous != device) e = cudaSetDevice(device);
@@ -281,9 +292,9 @@ static cudaError_t gather_scratch_of(int device, unsigned int** out) {
       if (e == cudaSuccess) e = back;
     }
     if (e != cudaSuccess) return e;
-    g_gather_scratch[device] = static_cast<unsigned int*>(address);
+    g_gather_scratch[device].store(static_cast<unsigned int*>(address), std::memory_order_release);
   }
-  *out = g_gather_scratch[device];
+  *out = g_gather_scratch[device].load(std::memory_order_acquire);
   return cudaSuccess;
 }
 
@@ -293,6 +304,12 @@ int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, co
                                        int slot, int out_kind, int M, int N, int K, void* stream) {
   if (!devices || world < 1 || world > dg::kMaxRanks || channel < 0 || channel >= DG_NOALLOC_CHANNELS)
     return (int)cudaErrorInvalidValue;   // more ranks or channels than the built-in counters cover
+  // Only the waiting forms: a signal-only call (slot 2, 3) would leave arrivals on counters that no caller can
+  // reach to collect, and the channel's next waiting call would then end before its data has landed.
+  if (slot != 0 && slot != 1) return (int)cudaErrorInvalidValue;
+  int current = -1;
+  if (rank < 0 || rank >= world || cudaGetDevice(&current) != cudaSuccess || current != devices[rank])
+    return (int)cudaErrorInvalidValue;   // the kernel counts its CTAs on the current device's block
   void* flags[dg::kMaxRanks];
   for (int q = 0; q < world; ++q) {
     unsigned int* base = nullptr;
@@ -360,6 +377,20 @@ int dg_take_status(void) {
   if (e == cudaSuccess) e = cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost);
   if (e == cudaSuccess && word) e = cudaMemset(st->status, 0, sizeof(int));
   return e == cudaSuccess ? word : -(int)e;
+}
+
+int dg_reset_noalloc_channel(int channel, void* stream) {
+  if (channel < 0 || channel >= DG_NOALLOC_CHANNELS) return (int)cudaErrorInvalidValue;
+  int current = 0;
+  cudaError_t e = cudaGetDevice(&current);
+  unsigned int* base = nullptr;
+  if (e == cudaSuccess) e = gather_scratch_of(current, &base);
+  if (e != cudaSuccess) return (int)e;
+  return dg_reset_counters(base + 4 * channel, stream);
+}
+
+unsigned long long dg_set_wait_limit_ns(unsigned long long limit_ns) {
+  return g_wait_limit_ns.exchange(limit_ns ? limit_ns : dg::kWaitLimitNs, std::memory_order_relaxed);
 }
 
 int dg_set_static_weights(int enabled) {

@@ -42,7 +42,8 @@ constexpr int kMaxStages = 12;
 constexpr int kStepBytes = 512;            // 32 lanes x 16 bytes of one weight row
 constexpr int kSmemHeader = 256;           // mbarriers + abort flag
 constexpr int kSmemLimit = 232448;         // 227 KB of dynamic shared memory per CTA on sm_100
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // bounded waits: after 2 s give up, flag it, leave
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // bounded waits give up after this (default; the host
+                                                             // can set another limit, Params::wait_limit_ns)
 
 // status word bits written on a wait that ran out (never expected; the host can read the word)
 constexpr int kStatusProducerTimeout = 1;
@@ -137,7 +138,9 @@ struct Params {
   int stage_bytes;           // bytes of one ring stage
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
   int early_weights;         // 1: weight copies may be issued before the previous kernel of the stream completed
+  int split_tail;            // 1: a short last tile and the tile before it are walked as two equal tiles (see Walk)
   unsigned long long* trace; // diagnostic (dg_set_trace): kTraceSlots time stamps per CTA, or null
+  unsigned long long wait_limit_ns;   // every wait in the kernel gives up after this long (status word, then leaves)
   // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results go into slot `rank` of its own
   // [world][M][N] buffer; every CTA then copies its rows to the same slot of every other rank's buffer (peer_out[q],
   // peer-mapped addresses) and counts itself done in word 2 of this rank's counter block; the last CTA adds 1 to
@@ -178,6 +181,14 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
 // Two FP32 values in one 64-bit register pair, the operand form of the packed fma.rn.f32x2 / mul.rn.f32x2. Operands
 // are packed once where they are produced and accumulators stay packed across the whole K loop, so that no
 // pack / unpack moves surround the FMAs (measured: almost one extra instruction per packed FMA otherwise).
+#ifdef DG_SCALAR_PAIRS   // experiment: the pair as two registers, advanced by two scalar FMAs
+struct pk2 { float lo, hi; };
+__device__ __forceinline__ pk2 pack2(float lo, float hi) { pk2 r; r.lo = lo; r.hi = hi; return r; }
+__device__ __forceinline__ pk2 pack2_bits(uint32_t lo, uint32_t hi) { return pack2(__uint_as_float(lo), __uint_as_float(hi)); }
+__device__ __forceinline__ float sum2(pk2 a) { return a.lo + a.hi; }
+__device__ __forceinline__ pk2 ffma2(pk2 a, pk2 b, pk2 c) { return pack2(fmaf(a.lo, b.lo, c.lo), fmaf(a.hi, b.hi, c.hi)); }
+__device__ __forceinline__ pk2 fmul2(pk2 a, pk2 b) { return pack2(a.lo * b.lo, a.hi * b.hi); }
+#else
 struct pk2 { unsigned long long v; };
 __device__ __forceinline__ pk2 pack2(float lo, float hi) {
   pk2 r;
@@ -205,6 +216,7 @@ __device__ __forceinline__ pk2 fmul2(pk2 a, pk2 b) {
   return d;
 }
 
+#endif
 // The same two chains as two plain FP32 registers, for the kernels that advance them with the mixed-precision FMA
 // (16-bit operands, FP32 addend and result, one rounding: fma.rn.f32.bf16 / fma.rn.f32.f16). The product of two 16-bit
 // operands is exact in FP32, so the result is bit for bit that of the FP32 FMA on the converted operands; what the
@@ -263,6 +275,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#ifdef DG_WAIT_HINT
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(DG_WAIT_HINT)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -270,6 +291,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok != 0;
 }
 // Bounded wait. False when it gave up or another thread of the CTA already had: the caller leaves its loops.
@@ -281,13 +303,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
 __device__ __forceinline__ void trace_stamp(unsigned long long* trace, int slot) {   // the latest stamp of a slot wins
   if (trace) atomicMax(trace + (size_t)blockIdx.x * kTraceSlots + slot, global_ns());
 }
+// The limit sits in shared memory right after the abort flag (written once by the kernel's first thread).
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   const unsigned long long start = global_ns();
+  const unsigned long long limit = *reinterpret_cast<const volatile unsigned long long*>(abort_flag + 2);
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_ns() - start > kWaitLimitNs) break;
+      if (global_ns() - start > limit) break;
     }
   }
   *abort_flag = 1;
@@ -357,13 +381,35 @@ __device__ __forceinline__ void store_out(void* out, int kind, size_t idx, float
 template <int CW>
 struct Walk {
   int lo, hi, tile_rows, ntiles, nwin, win_bytes;
+  int split_row0, split_first;   // split tail: first row and height of the last-but-one tile (split_first = 0: none)
   __device__ __forceinline__ Walk(const Params& p) {
     lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
     hi = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
     tile_rows = CW * p.rows_per_warp;
     ntiles = (hi - lo + tile_rows - 1) / tile_rows;
+    // A short last tile walks every K window for a few rows: with only `stages` windows in flight and almost no
+    // bytes in each, it runs at DRAM latency, not bandwidth. For one activation row (the only case where it
+    // measured faster: 8192 x 28672 NVFP4 45.5 -> 41.1 us) the last full tile and a remainder under a quarter of a
+    // tile are therefore walked as two tiles of equal height (48 + 7 -> 28 + 27).
+    split_first = 0;
+    split_row0 = 0;
+    const int rows = hi - lo, rem = rows % tile_rows;
+    if (p.split_tail && rows > tile_rows && rem > 0 && 4 * rem < tile_rows) {
+      split_row0 = lo + (ntiles - 2) * tile_rows;
+      split_first = (tile_rows + rem + 1) / 2;
+    }
     win_bytes = p.steps * kStepBytes;
     nwin = (p.row_bytes + win_bytes - 1) / win_bytes;
+  }
+  // First row and height of tile t.
+  __device__ __forceinline__ void tile(int t, int& row0, int& rows) const {
+    if (split_first && t >= ntiles - 2) {
+      row0 = t == ntiles - 2 ? split_row0 : split_row0 + split_first;
+      rows = t == ntiles - 2 ? split_first : hi - row0;
+    } else {
+      row0 = lo + t * tile_rows;
+      rows = min(tile_rows, hi - row0);
+    }
   }
 };
 
@@ -426,8 +472,8 @@ struct Producer {
   // cp.async arrivals are outstanding).
   __device__ __forceinline__ void weights(int it, int s) const {
     const int t = it / wk.nwin, win = it - t * wk.nwin;
-    const int row0 = wk.lo + t * wk.tile_rows;
-    const int rows = min(wk.tile_rows, wk.hi - row0);
+    int row0, rows;
+    wk.tile(t, row0, rows);
     const uint32_t full = full0 + 8u * s;
     const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
     const int byte0 = win * wk.win_bytes;
@@ -1107,7 +1153,7 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
     unsigned int seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine + p.gather_slot) : "memory");
     done = seen >= want;
-    if (!done && (i & 63u) == 0u && (*abort_flag || global_ns() - start > kWaitLimitNs)) break;
+    if (!done && (i & 63u) == 0u && (*abort_flag || global_ns() - start > p.wait_limit_ns)) break;
   }
   if (done)
     asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mine + p.gather_slot), "r"(0u - want) : "memory");
@@ -1137,6 +1183,7 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
       mbar_init(empty0 + 8u * s, CW);
     }
     *abort_flag = 0;
+    *reinterpret_cast<volatile unsigned long long*>(abort_flag + 2) = p.wait_limit_ns;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -1167,12 +1214,17 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
     uint32_t parity = 0;
     bool ok = true;
     for (int t = 0; t < wk.ntiles && ok; ++t) {
-      const int row0 = wk.lo + t * wk.tile_rows;
-      const int rows = min(wk.tile_rows, wk.hi - row0);
+      int row0, rows;
+      wk.tile(t, row0, rows);
       const int nr = rows > warp ? (rows - warp + CW - 1) / CW : 0;
-      if (nr > 2)
+      // three rows have their own code only where tiles of odd heights are made on purpose (split tails)
+      constexpr bool THREE = M == 1 && RMAX == 4;
+      if (nr > (THREE ? 3 : 2))
         ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
                                                       it);
+      else if (THREE && nr > 2)
+        ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr,
+                                                                 s, parity, it);
       else if (nr > 1)
         ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
                                                       it);

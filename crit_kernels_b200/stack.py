@@ -70,40 +70,77 @@ class StackRun:
     def __init__(self, stack, m):
         self.stack, self.m = stack, m
         dev = stack.device
-        g = torch.Generator().manual_seed(4242 + m)
+        # the first m rows of one seeded 16-row batch per role, so that row i is the same activation at every m and
+        # the row-count invariance of the outputs can be checked across passes
+        g = torch.Generator().manual_seed(4242)
         pin = (lambda t: t.pin_memory()) if dev.type == "cuda" else (lambda t: t)
-        self.x_host = {role: pin(torch.randn(m, k, generator=g).to(torch.bfloat16)) for role, k, _ in stack.roles}
+        self.x_host = {role: pin(torch.randn(16, k, generator=g).to(torch.bfloat16)[:m].contiguous())
+                       for role, k, _ in stack.roles}
         self.x = {role: t.to(dev) for role, t in self.x_host.items()}
         self.shard = {role: torch.empty(m, n // stack.world, dtype=torch.bfloat16, device=dev)
                       for role, _, n in stack.roles}
-        self.fused = FusedGatherBuffers(stack, m) if stack.world > 1 and stack.gather.startswith("fused") else None
+        # Gathered buffers. A rank may start storing pass k + 1 into its peers' buffers while they still read what pass
+        # k gathered (see the reuse rule in include/decode_gemv_b200.h): with waiting gathers every call is ordered
+        # behind the peers' previous calls and one set is safe for this stack; with signal-only gathers nothing
+        # orders a fast rank's next pass behind a peer's reads, so passes alternate between two sets.
+        fused = stack.world > 1 and stack.gather.startswith("fused")
+        sets = 2 if fused and stack.gather == "fused-overlap" else 1
+        self.fused_sets = [FusedGatherBuffers(stack, m) for _ in range(sets)] if fused else []
+        self.passes = 0                     # passes enqueued (eager or captured): picks the set of the next one
         self.calls = 0
-        self.pending = [0, 0]
-        self.full = self.fused.full if self.fused else {
+        self.pending = [[0, 0] for _ in range(max(sets, 1))]
+        self.plain_full = None if fused else {
             role: torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16, device=dev)
             for role, _, n in stack.roles}
-        last = stack.roles[-1][0]
-        self.out_host = pin(torch.empty_like(self.full[last], device="cpu"))
+        self.out_host = {role: pin(torch.empty(stack.world, m, n // stack.world, dtype=torch.bfloat16))
+                         for role, _, n in stack.roles}
         self.h2d_bytes = sum(t.numel() * 2 for t in self.x_host.values())
-        self.d2h_bytes = self.out_host.numel() * 2
+        self.d2h_bytes = sum(t.numel() * 2 for t in self.out_host.values())
         self.kernel_launches = len(stack.projections)
-        self.graph = None
+        self.graphs = []
+        self.replays = 0
+
+    @property
+    def fused(self):
+        """The gathered buffers of the pass being enqueued."""
+        return self.fused_sets[self.passes % len(self.fused_sets)] if self.fused_sets else None
+
+    @property
+    def full(self):
+        """Every role's gathered buffer [P][M][N/P] as the last completed pass left it."""
+        if not self.fused_sets:
+            return self.plain_full
+        return self.fused_sets[(self.passes - 1) % len(self.fused_sets)].full
 
     def eager(self, keep=None):
         """Runs the pass on the current stream; `keep` collects every projection's gathered [M][N] output."""
         st = self.stack
+        previous = None
+        if st.device.type == "cuda":       # the stack's weights are resident: scope the static-weights setting
+            from . import cabi
+            previous = cabi.load().dg_set_static_weights(1 if st.static_weights else 0)
+        try:
+            self._pass(keep)
+        finally:
+            if previous is not None:
+                cabi.load().dg_set_static_weights(previous)
+        self.passes += 1
+
+    def _pass(self, keep):
+        st = self.stack
+        full = self.fused.full if self.fused else self.plain_full
         for p in st.projections:
             if self.fused:
                 self._gemv_allgather(p, overlap=st.gather == "fused-overlap")
             else:
                 st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
                 if st.world > 1:
-                    st.nccl_gather(self.full[p.role], self.shard[p.role])
+                    st.nccl_gather(full[p.role], self.shard[p.role])
             if st.world > 1:
                 if keep is not None:
                     if self.fused and st.gather == "fused-overlap":
                         self._collect()              # a test reads this projection's output now
-                    keep.append(self.full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone())
+                    keep.append(full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone())
             elif keep is not None:
                 keep.append(self.shard[p.role].clone())
         if self.fused and st.gather == "fused-overlap":
@@ -114,13 +151,14 @@ class StackRun:
         from . import cabi
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         base = ctypes.c_void_p(self.fused.arena.data_ptr())
+        pending = self.pending[self.passes % len(self.fused_sets)]
         for slot in (0, 1):
-            calls = self.pending[slot]
+            calls = pending[slot]
             if calls:
                 code = cabi.load().dg_enqueue_gather_wait(base, slot, calls * self.stack.world, stream)
                 if code:
                     raise RuntimeError(f"dg_enqueue_gather_wait: cudaError {code}")
-                self.pending[slot] = 0
+                pending[slot] = 0
 
     def _gemv_allgather(self, p, overlap=False):
         """The GEMV with the all-gather in its epilogue (C ABI dg_enqueue_nvfp4_allgather) on the current stream."""
@@ -135,7 +173,7 @@ class StackRun:
         if code:
             raise RuntimeError(f"dg_enqueue_nvfp4_allgather: cudaError {code}")
         if overlap:
-            self.pending[self.calls & 1] += 1
+            self.pending[self.passes % len(self.fused_sets)][self.calls & 1] += 1
         self.calls += 1
 
     def capture(self):
@@ -146,21 +184,35 @@ class StackRun:
                 self.eager()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.eager()
+        # one graph per set of gathered buffers; replays take them in turn (an even number of warm-up passes above,
+        # so the first graph is captured on set 0)
+        for _ in range(max(len(self.fused_sets), 1)):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.eager()
+            self.graphs.append(graph)
+        self.passes = 0
         return self
 
     def replay(self):
-        self.graph.replay()
+        self.graphs[self.replays % len(self.graphs)].replay()
+        self.replays += 1
+        self.passes = self.replays
+
+    def outputs(self):
+        """Every role's output [M][N] of the last completed pass (the last layer's, since layers share buffers)."""
+        if self.stack.world > 1:
+            return {role: self.full[role].permute(1, 0, 2).reshape(self.m, -1) for role, _, _ in self.stack.roles}
+        return {role: self.shard[role] for role, _, _ in self.stack.roles}
 
     def replay_e2e(self):
+        """A pass as a caller with host buffers sees it: activations up, the pass, every role's output down."""
         for role, host in self.x_host.items():
             self.x[role].copy_(host, non_blocking=True)
-        self.graph.replay()
-        last = self.stack.roles[-1][0]
-        src = self.full[last] if self.stack.world > 1 else self.shard[last].view_as(self.out_host)
-        self.out_host.copy_(src, non_blocking=True)
+        self.replay()
+        for role, _, _ in self.stack.roles:
+            src = self.full[role] if self.stack.world > 1 else self.shard[role].view_as(self.out_host[role])
+            self.out_host[role].copy_(src, non_blocking=True)
         torch.cuda.synchronize()
 
 
@@ -174,6 +226,9 @@ class ShardedStack:
     group: object = None
     kernel: object = None
     gather: str = "fused"       # "fused": all-gather in the GEMV epilogue over symmetric memory; "nccl": NCCL per GEMV
+    static_weights: bool = True
+    seed: int = 0
+    layers: int = 0
 
     @property
     def gather_kind(self):
@@ -193,9 +248,11 @@ class ShardedStack:
     @classmethod
     def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None, gather="fused",
                static_weights=True):
-        """`layers` x `roles` projections; static_weights: the stack's weights are resident and never rewritten, so
-        every GEMV may start streaming them while the kernel before it finishes (dg_set_static_weights); every rank draws the same full matrix from the same seed and keeps its
-        rows, so the shards of all ranks together are exactly the matrix a single GPU would hold."""
+        """`layers` x `roles` projections. static_weights: the stack's weights are resident and never rewritten, so
+        every GEMV of a pass may start streaming them while the kernels before it finish (dg_set_static_weights is
+        switched on for the duration of each enqueued pass and restored after it). Every rank draws the same full
+        matrix from the same seed and keeps its rows, so the shards of all ranks together are exactly the matrix a
+        single GPU would hold."""
         projections = []
         for layer in range(layers):
             for idx, (role, k, n) in enumerate(roles):
@@ -209,10 +266,15 @@ class ShardedStack:
                 del codes, scales, inverse
         if gather not in ("fused", "fused-overlap", "nccl"):
             raise ValueError(f"gather must be 'fused', 'fused-overlap' or 'nccl', not {gather!r}")
-        if device.type == "cuda":
-            from . import cabi
-            cabi.load().dg_set_static_weights(1 if static_weights else 0)
-        return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel(), gather)
+        return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel(), gather,
+                   static_weights, seed, layers)
+
+    @staticmethod
+    def full_matrix(seed, layer, idx, role_k_n, device):
+        """The whole (unsharded) matrix of projection `idx` of `layer`, as every rank draws it before keeping its rows."""
+        _, k, n = role_k_n
+        g = torch.Generator(device=device).manual_seed(seed * 1000003 + layer * 16 + idx)
+        return random_nvfp4(n, k, device, g)
 
     def capture(self, m):
         return StackRun(self, m).capture()

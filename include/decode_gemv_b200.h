@@ -47,7 +47,16 @@ DG_API int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t
  * ends only when every rank's results have arrived in this rank's buffer (bounded wait: dg_take_status bit 2 on
  * time-out). Consecutive calls alternate slot 0 and 1. With slot 2 or 3 the kernel uses counter slot - 2 and does
  * not wait: it only delivers its results and counts the rank in, so that GEMVs whose inputs do not depend on the
- * gathered outputs overlap their gathers; dg_enqueue_gather_wait then collects the arrivals. */
+ * gathered outputs overlap their gathers; dg_enqueue_gather_wait then collects the arrivals.
+ * When a gathered buffer may be written again: a rank starts storing call n + 1's results into its peers' buffers
+ * as soon as its own call n has ended, which only says that every rank has FINISHED COMPUTING call n, not that the
+ * peers have finished READING what call n gathered. So a buffer that call n filled must not be the target of call
+ * n + 1: alternate two buffers (as the counters alternate), after which call n + 2 may reuse the first, because no
+ * rank can start it before every rank has passed call n + 1, which is stream-ordered after that rank's readers of
+ * call n. With the signal-only form the same holds per collected batch: reuse a buffer only after every rank has
+ * passed a later waiting call or dg_enqueue_gather_wait (two sets of buffers, used in turn, satisfy it).
+ * After a time-out (status bit 2) the counters hold stray arrivals: re-zero them on every rank (dg_reset_counters)
+ * once all ranks are idle, before the next call. */
 DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
                                       int blocked, const float* inverse, void* const* peer_out,
                                       void* const* peer_flags, int world, int rank, int slot, int out_kind, int M,
@@ -58,6 +67,11 @@ DG_API int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, con
  * (calls made on that counter) x world arrivals and takes them off. When it has run, the results of all those calls
  * from every rank are in this rank's buffers. No counterpart in the reference. */
 DG_API int dg_enqueue_gather_wait(void* flags, int slot, unsigned int expected, void* stream);
+
+/* Zeroes a block of four counters in stream order (after a time-out, or before first use of memory that was not
+ * zero-filled). Every rank does this for its own block while no all-gather call of the group is in flight. No
+ * counterpart in the reference. */
+DG_API int dg_reset_counters(void* flags, void* stream);
 
 /* dg_enqueue_nvfp4_allgather for callers that cannot allocate device memory. No counterpart in the reference.
  *
@@ -73,10 +87,13 @@ DG_API int dg_enqueue_gather_wait(void* flags, int slot, unsigned int expected, 
  * ordinal of every rank (devices[q], host array of `world` ints) and a channel 0 .. DG_NOALLOC_CHANNELS - 1; rank q's
  * counters are block `channel` in device devices[q]'s copy of the library's array, so all ranks must live in
  * this process (one thread or stream per GPU) with peer access enabled between their devices; world = 1 needs
- * neither. More than 8 ranks or a channel outside the range is refused with cudaErrorInvalidValue (1): the built-in
- * counters cover nothing larger.
+ * neither. devices[rank] must be the current device. Only the waiting forms exist here (slot 0 or 1): arrivals
+ * left by a signal-only call could not be collected, since the built-in counters have no address the caller could
+ * hand to dg_enqueue_gather_wait. More than 8 ranks, a channel outside the range, slot 2 or 3, or a current device
+ * other than devices[rank] is refused with cudaErrorInvalidValue (1).
  * The first call that names a device looks up that device's array (cudaSetDevice + cudaGetSymbolAddress, then back):
- * make that first call outside any stream capture.
+ * make that first call outside any stream capture, and only name devices this process has already initialised
+ * (cudaSetDevice on a device without a context creates one, which allocates).
  * Every call on a channel shares its counters, which keep whatever the last call left: a completed call leaves
  * them zero, and that is the state the next call requires. Two calls on the same channel that overlap on the GPU, or a
  * call after one that timed out (dg_take_status bit 2), race on the counters; use another channel, or order them. */
@@ -85,6 +102,11 @@ DG_API int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_b
                                               const uint8_t* scales, int blocked, const float* inverse,
                                               void* const* peer_out, const int* devices, int world, int rank,
                                               int channel, int slot, int out_kind, int M, int N, int K, void* stream);
+
+/* Zeroes the current device's counters of a built-in channel in stream order: the way back to a usable channel after
+ * a call on it timed out (dg_take_status bit 2). Every rank calls it for its own device while the group is idle.
+ * Allocates nothing. No counterpart in the reference. */
+DG_API int dg_reset_noalloc_channel(int channel, void* stream);
 
 /* FP8 E4M3 W8A16. Replaces enqueue_gemv_fp8 (decode_gemv.h:34-36, decode_gemv.cu:402-417).
  * Exactly one of row_scale ([N] FP32: out = row_scale[n] * sum) and mx_scale ([N][K/32] E8M0 bytes, MXFP8:
@@ -117,18 +139,27 @@ DG_API int dg_hardware_decode(void);
  * [4] = bytes per stage, [5] = dynamic shared memory bytes. Host only; returns 0, or 1 for sizes the kernels refuse. */
 DG_API int dg_plan(int fmt, int M, int N, int K, int plan[6]);
 
-/* Reads and clears the current device's error word: bit 0 a producer wait ran out, bit 1 a consumer wait ran out
- * (a bounded wait inside a kernel gave up; the call's output is then incomplete). Synchronises the device. Host
- * diagnostic, not part of the hot path; returns the word (0 = clean) or a negative cudaError_t. */
+/* Reads and clears the current device's error word: bit 0 a producer wait ran out, bit 1 a consumer wait ran out,
+ * bit 2 a wait for all-gather arrivals ran out (a bounded wait inside a kernel gave up; the call's output is then
+ * incomplete). Synchronises the device. Host diagnostic, not part of the hot path; returns the word (0 = clean) or a
+ * negative cudaError_t. */
 DG_API int dg_take_status(void);
 
-/* Tells the library whether weights (codes, block scales staged with them, BF16 weights) are static: never written
- * by the kernel that precedes a GEMV in its stream. Every GEMV kernel is launched with programmatic dependent launch,
- * i.e. it may start while the previous kernel of the stream finishes; it always waits for that kernel before it reads
- * activations, row / inverse scales or directly-read block scales and before it writes. With enabled = 1 it starts
- * streaming weights before that wait, which hides its start-up behind the previous kernel's tail (what a decode
- * stack with resident weights wants); with 0 (the default) nothing is read before the wait, which is correct for
- * any caller. Process-wide; returns the previous setting. No counterpart in the reference. */
+/* Sets how long any wait inside the kernels may last before it gives up (nanoseconds; 0 restores the default of
+ * 2 s) and returns the previous limit. Applies to launches enqueued afterwards; process-wide. A serving process
+ * that detects a lost peer on the host can keep this short so that the GPU side returns promptly with status bit 2
+ * instead of holding the stream for seconds. No counterpart in the reference. */
+DG_API unsigned long long dg_set_wait_limit_ns(unsigned long long limit_ns);
+
+/* Tells the library whether weights (codes, block scales staged with them, BF16 weights) are static: not written by
+ * any kernel of the stream that can still be in flight when a GEMV starts. Every GEMV kernel is launched with
+ * programmatic dependent launch and lets its own successor start at once, so a GEMV may begin while the kernel before
+ * it, and in a run of GEMVs the ones before that, are still finishing; it always waits for all of them before it
+ * reads activations, row / inverse scales or directly-read block scales and before it writes. With enabled = 1 it
+ * starts streaming weights before that wait, which hides its start-up behind the previous kernels' tails (what a
+ * decode stack with resident weights wants); with 0 (the default) nothing is read before the wait, which is correct
+ * for any caller. The setting is read when a call is enqueued (a captured graph keeps what it was captured with).
+ * Process-wide; returns the previous setting, so a caller can scope it. No counterpart in the reference. */
 DG_API int dg_set_static_weights(int enabled);
 
 /* Diagnostic: where a launch's time goes. `buffer` is zero-filled device memory for `launches` regions of

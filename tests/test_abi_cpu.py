@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared_symbols():
     with open(os.path.join(ROOT, "include", "decode_gemv_b200.h")) as f:
-        return re.findall(r"DG_API\s+int\s+(dg_\w+)\s*\(", f.read())
+        return re.findall(r"DG_API\s+(?:unsigned\s+long\s+long|int)\s+(dg_\w+)\s*\(", f.read())
 
 
 def test_library_exports_every_declared_symbol():

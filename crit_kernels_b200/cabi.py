@@ -19,6 +19,8 @@ SIGNATURES = {
     "dg_enqueue_fp8": (_i, [_p, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_dequantize": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
+    "dg_enqueue_quantize_fp8_rows": (_i, [_p, ctypes.c_longlong, _i, _i, _p, ctypes.c_longlong, _p, _p]),
+    "dg_enqueue_quantize_nvfp4": (_i, [_p, ctypes.c_longlong, _i, _i, ctypes.c_float, ctypes.c_float, _p, _p, _p]),
     "dg_hardware_decode": (_i, []),
     "dg_plan": (_i, [_i, _i, _i, _i, _f]),
     "dg_take_status": (_i, []),

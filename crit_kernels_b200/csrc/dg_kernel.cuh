@@ -111,7 +111,9 @@ __host__ __device__ constexpr int producer_warps(int fmt, int m) {
 // half a slot per product plus the conversions. MXFP8 stays on the FP32 path: its weights carry their block scale,
 // and weight x 2^(e - 127) is not always a BF16 value.
 __host__ __device__ constexpr bool use_mixed(int fmt, int m) {
-  return fmt != FMT_MXFP8 && (shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && fmt != FMT_FP8));
+  return fmt != FMT_MXFP8 && (shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && fmt != FMT_FP8) ||
+                              (fmt == FMT_BF16 && m <= 2));   // BF16 weights need no conversion at all: M FMAs per
+                                                              // weight against 1 + M / 2 instructions packed
 }
 // Rows a consumer warp holds at once (register budget).
 __host__ __device__ constexpr int rows_max(int fmt, int m) {

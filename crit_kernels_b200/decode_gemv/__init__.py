@@ -1,23 +1,27 @@
-"""Decode GEMVs for B200, weight only: NVFP4 weights (W4A16), FP8 E4M3 weights with a row scale or MXFP8's E8M0 scale
-per 32 inputs (W8A16) and BF16 weights, times 1 to 16 rows of 16-bit activations, on CUDA cores with FP32 sums. Each
-row's result is the same bits alone and beside the other rows of a call, and the same bits from any slice of the
-matrix's rows: the summation order depends on K and the format only.
+"""Weight-only decode projections for B200: y = x W^T for 1 to 16 activation rows x (BF16 or FP16) and a weight matrix
+W kept in its checkpoint format: NVFP4 (4-bit E2M1 codes with an E4M3 scale per 16 inputs), FP8 E4M3 with one FP32
+scale per output channel, MXFP8 (E4M3 with a power-of-two E8M0 scale per 32 inputs) or plain BF16. The products are
+summed in FP32 on CUDA cores in an order that depends only on K and the format, so an output row has the same bits
+whether it is computed alone, among other rows, or from a slice of W's rows on another GPU.
 
-Same functions, argument layouts and refusals as the reference package's CUDA entry points
-(decode-gemv/torch-ext/decode_gemv/__init__.py:19-53), plus the NVFP4 dequantizers decode and decode_fp8, which the
-reference implements in Triton (triton_gemv.py:171-200) and this package in CUDA. The reference's other Triton entry
-points (gemv_triton, gemv_fp8_dot, ...) are not part of this package.
+This module is what `get_kernel("crit-labs/decode-gemv")` hands out: `gemv`, `gemv_fp8`, `gemv_bf16`,
+`hardware_decode` and `CUDA_ROWS` take the arguments of the reference package's functions of those names
+(decode-gemv/torch-ext/decode_gemv/__init__.py:19-53) and refuse what they refuse. Beyond that surface it carries the
+pieces either side of the GEMVs that the reference keeps elsewhere: `decode` / `decode_fp8` (its Triton dequantizers,
+triton_gemv.py:171-200, here in CUDA) and `quantize_fp8_rows` / `quantize_nvfp4` (the activation quantizers of its
+mma-rows package). The reference's Triton GEMVs (gemv_triton, gemv_fp8_dot and their helpers) have no counterpart here.
 
-NVFP4 matrices as checkpoints store them: codes [N][K / 2] uint8 (element 2i in the low nibble of byte i), E4M3 block
-scales [N][K / 16] (row major, or cuBLASLt's 128 x 4 tiles with blocked=True) and inverse [N] FP32 (one over each row's
-global scale). FP8: codes [N][K] E4M3 and FP32 row scales [N], or E8M0 bytes [N][K / 32] (MXFP8)."""
+Storage: NVFP4 codes [N][K / 2] uint8 with input 2i in the low nibble of byte i, block scales [N][K / 16] E4M3 either
+row major or, with blocked=True, in cuBLASLt's 128 x 4 tiles, and inverse [N] FP32 = 1 / the row's global scale; FP8
+codes [N][K] with FP32 scales [N], or with E8M0 bytes [N][K / 32] for MXFP8."""
 import torch
 
 from ._ops import ops
 
 CUDA_ROWS = 16   # rows the GEMVs take in one call
 
-__all__ = ["CUDA_ROWS", "gemv", "gemv_fp8", "gemv_bf16", "hardware_decode", "decode", "decode_fp8"]
+__all__ = ["CUDA_ROWS", "gemv", "gemv_fp8", "gemv_bf16", "hardware_decode", "decode", "decode_fp8", "quantize_fp8_rows",
+           "quantize_nvfp4"]
 
 _TRITON_SIDE = {"DOT_ROWS", "TRITON_ROWS", "dot_partial_elements", "fp8_dot_tile", "gemv_fp8_dot", "gemv_triton",
                 "hardware"}
@@ -25,30 +29,31 @@ _TRITON_SIDE = {"DOT_ROWS", "TRITON_ROWS", "dot_partial_elements", "fp8_dot_tile
 
 def gemv(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, inverse: torch.Tensor, out: torch.Tensor,
          blocked: bool = False):
-    """out [M][N] (FP32 or x's dtype) = x [M][K] (M 1..16, BF16 or FP16, rows on 16-byte boundaries, K a multiple of
-    32) times the NVFP4 matrix. blocked: the E4M3 block scales are in cuBLASLt's 128 x 4 tiled layout (rows padded to
-    128, blocks to 4) instead of row major [N][K / 16]. Returns out."""
+    """NVFP4 projection. Writes x @ W^T into out and returns it. x: [M][K], 1 <= M <= 16, BF16 or FP16, every row on
+    a 16-byte boundary, K % 32 == 0. out: [M][N], FP32 or x's dtype. Pass blocked=True when `scales` uses the
+    128 x 4 tiled layout (128-row, 4-block padding) rather than plain [N][K / 16]."""
     ops.gemv(x, codes, scales, inverse, blocked, out)
     return out
 
 
 def gemv_fp8(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, out: torch.Tensor):
-    """out [M][N] (FP32 or x's dtype) = x [M][K] (M 1..16, BF16 or FP16) times the FP8 matrix: codes [N][K] E4M3
-    (float8_e4m3fn or uint8, K a multiple of 16) with scales FP32 [N] (one per row, applied after the sum) or uint8
-    E8M0 [N][K / 32] (MXFP8, each value times its power of two). Returns out."""
+    """FP8 projection. Writes x @ W^T into out and returns it. codes: [N][K] E4M3 (float8_e4m3fn or raw uint8),
+    K % 16 == 0. The dtype of `scales` picks the flavour: FP32 [N] multiplies each finished sum by its channel's
+    scale; uint8 [N][K / 32] are MXFP8 exponents, each weight counting 2^(e - 127) times its code (K % 32 == 0)."""
     ops.gemv_fp8(x, codes.view(torch.uint8), scales, out)
     return out
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
-    """out [M][N] (FP32 or BF16) = x [M][K] (M 1..16, BF16) times w [N][K] BF16 (K a multiple of 8). Returns out."""
+    """BF16 projection, the pure bandwidth case. x [M][K] and w [N][K] BF16, K % 8 == 0; out [M][N] FP32 or BF16,
+    returned."""
     ops.gemv_bf16(x, w, out)
     return out
 
 
 def hardware_decode(device=None) -> bool:
-    """Whether the GEMV's code for `device` decodes E2M1 by the hardware conversion: always, on the sm_100a target
-    this package is built for."""
+    """True when E2M1 codes are decoded by the conversion instruction rather than by bit arithmetic on `device`.
+    This build targets sm_100a only, where that is always so; a device it cannot run on raises RuntimeError."""
     device = torch.device(device or "cuda")
     return bool(ops.hardware_decode(torch.empty(0, device=device)))
 
@@ -70,6 +75,23 @@ def decode_fp8(codes: torch.Tensor, scales: torch.Tensor, factor: torch.Tensor, 
         raise RuntimeError(f"decode_fp8: out must be float8_e4m3fn, got {out.dtype}")
     ops.decode(codes, scales, factor, out)
     return out
+
+
+def quantize_fp8_rows(x: torch.Tensor, q: torch.Tensor, scale: torch.Tensor):
+    """BF16 rows to FP8: q [rows][K] (float8_e4m3fn or uint8) = x / scale rounded to E4M3, with scale [rows] FP32 =
+    max(|row|) / 448 (at least 1e-12) written too. Any number of rows and any K. The arithmetic and bits of the
+    reference's mma_rows.quantize_fp8_rows (mma-rows/torch-ext/mma_rows/__init__.py:124-128). Returns (q, scale)."""
+    ops.quantize_fp8_rows(x, q.view(torch.uint8), scale)
+    return q, scale
+
+
+def quantize_nvfp4(x: torch.Tensor, input_scale: float, codes: torch.Tensor, scales: torch.Tensor):
+    """BF16 rows to NVFP4 under `input_scale`: codes [rows][K / 2] (two E2M1 codes a byte, the even input low) and one
+    E4M3 scale per 16 inputs, stored in 128 x 4 tiles with rows padded to 128 and blocks to 4 (padding zeroed).
+    K % 16 == 0. The bits of the reference's mma_rows.quantize_nvfp4 (mma-rows/torch-ext/mma_rows/__init__.py:131-136).
+    Returns (codes, scales)."""
+    ops.quantize_nvfp4(x, float(input_scale), codes.view(torch.uint8), scales.view(torch.uint8))
+    return codes, scales
 
 
 def __getattr__(name):

@@ -168,8 +168,59 @@ void decode(const torch::Tensor& codes, const torch::Tensor& scales, const torch
 }
 
 int64_t hardware_decode(const torch::Tensor& device_of) {
+  TORCH_CHECK(device_of.is_cuda(), "hardware_decode: the tensor names a CUDA device");
   const c10::cuda::CUDAGuard guard(device_of.device());
-  return dg_hardware_decode();
+  const int answer = dg_hardware_decode();
+  TORCH_CHECK(answer >= 0, "hardware_decode: ", device_of.device(), " cannot run this library (built for sm_100a only)");
+  return answer;
+}
+
+// Any number of BF16 rows (the quantizers serve prompts as well as decode steps).
+void require_rows_to_quantize(const torch::Tensor& x, const char* op) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.size(0) >= 1, op,
+              ": x must be a 2-D BF16 CUDA tensor [rows][K] with at least one row");
+  TORCH_CHECK(x.stride(1) == 1 && x.stride(0) % 8 == 0 && on_boundary(x, 16), op,
+              ": rows of x must be contiguous and start on 16-byte boundaries");
+}
+
+void quantize_fp8_rows(const torch::Tensor& x, torch::Tensor& q, torch::Tensor& scale) {
+  const char* op = "quantize_fp8_rows";
+  require_rows_to_quantize(x, op);
+  const int64_t rows = x.size(0), k = x.size(1);
+  TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.element_size() == 1 && q.size(0) == rows && q.size(1) == k &&
+                  q.stride(1) == 1,
+              op, ": q must hold one byte per value, [rows][K] with contiguous rows");
+  TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == torch::kFloat32 && scale.is_contiguous() &&
+                  scale.numel() == rows,
+              op, ": scale must be contiguous FP32 [rows]");
+  require_same_device(x, {&q, &scale}, op);
+  const c10::cuda::CUDAGuard guard(x.device());
+  require_success(dg_enqueue_quantize_fp8_rows(x.data_ptr(), x.stride(0), static_cast<int>(rows), static_cast<int>(k),
+                                               static_cast<std::uint8_t*>(q.data_ptr()), q.stride(0),
+                                               scale.data_ptr<float>(), at::cuda::getCurrentCUDAStream().stream()),
+                  op);
+}
+
+void quantize_nvfp4(const torch::Tensor& x, double input_scale, torch::Tensor& codes, torch::Tensor& scales) {
+  const char* op = "quantize_nvfp4";
+  require_rows_to_quantize(x, op);
+  const int64_t rows = x.size(0), k = x.size(1);
+  TORCH_CHECK(k >= 16 && k % 16 == 0, op, ": K must be a multiple of 16, got ", k);
+  TORCH_CHECK(input_scale > 0, op, ": the input scale must be positive");
+  TORCH_CHECK(codes.is_cuda() && codes.element_size() == 1 && codes.is_contiguous() &&
+                  codes.numel() == rows * (k / 2) && on_boundary(codes, 8),
+              op, ": codes must be contiguous bytes [rows][K / 2] on an 8-byte boundary");
+  const int64_t tiled = ((rows + 127) / 128) * 128 * (((k / 16) + 3) / 4) * 4;
+  TORCH_CHECK(scales.is_cuda() && scales.element_size() == 1 && scales.is_contiguous() && scales.numel() == tiled, op,
+              ": scales must be ", tiled, " bytes: [rows][K / 16] in 128 x 4 tiles, rows padded to 128 and blocks to 4");
+  require_same_device(x, {&codes, &scales}, op);
+  const float g = static_cast<float>(input_scale);
+  const c10::cuda::CUDAGuard guard(x.device());
+  require_success(dg_enqueue_quantize_nvfp4(x.data_ptr(), x.stride(0), static_cast<int>(rows), static_cast<int>(k), g,
+                                            1.0f / g, static_cast<std::uint8_t*>(codes.data_ptr()),
+                                            static_cast<std::uint8_t*>(scales.data_ptr()),
+                                            at::cuda::getCurrentCUDAStream().stream()),
+                  op);
 }
 
 TORCH_LIBRARY(DG_TORCH_NAMESPACE, ops) {
@@ -178,6 +229,9 @@ TORCH_LIBRARY(DG_TORCH_NAMESPACE, ops) {
   ops.def("gemv_bf16(Tensor x, Tensor w, Tensor! out) -> ()");
   ops.def("hardware_decode(Tensor device_of) -> int");
   ops.def("decode(Tensor codes, Tensor scales, Tensor factor, Tensor! out) -> ()");
+  // the activation quantizers of the reference's mma-rows package, same schemas (mma-rows/torch-ext/torch_binding.cpp:11-12)
+  ops.def("quantize_fp8_rows(Tensor x, Tensor! q, Tensor! scale) -> ()");
+  ops.def("quantize_nvfp4(Tensor x, float input_scale, Tensor! codes, Tensor! scales) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(DG_TORCH_NAMESPACE, CUDA, ops) {
@@ -186,4 +240,6 @@ TORCH_LIBRARY_IMPL(DG_TORCH_NAMESPACE, CUDA, ops) {
   ops.impl("gemv_bf16", &gemv_bf16);
   ops.impl("hardware_decode", &hardware_decode);
   ops.impl("decode", &decode);
+  ops.impl("quantize_fp8_rows", &quantize_fp8_rows);
+  ops.impl("quantize_nvfp4", &quantize_nvfp4);
 }

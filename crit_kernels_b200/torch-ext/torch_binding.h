@@ -18,3 +18,8 @@ int64_t hardware_decode(const torch::Tensor& device_of);
 // product rounded once (FP8: saturating at +-448). codes [N][K / 2] uint8, scales [N][K / 16] E4M3 bytes, factor [N]
 // FP32. The reference's decode and decode_fp8 (decode-gemv/torch-ext/decode_gemv/triton_gemv.py:171-176, :195-200).
 void decode(const torch::Tensor& codes, const torch::Tensor& scales, const torch::Tensor& factor, torch::Tensor& out);
+// Activation quantizers (the reference's mma-rows package, mma-rows/torch-ext/torch_binding.h): x [rows][K] BF16, any
+// number of rows. FP8 per row: q [rows][K] E4M3 bytes, scale [rows] FP32. NVFP4: codes [rows][K / 2] bytes and E4M3
+// block scales in 128 x 4 tiles (rows padded to 128, blocks to 4) under input_scale.
+void quantize_fp8_rows(const torch::Tensor& x, torch::Tensor& q, torch::Tensor& scale);
+void quantize_nvfp4(const torch::Tensor& x, double input_scale, torch::Tensor& codes, torch::Tensor& scales);

@@ -129,6 +129,25 @@ DG_API int dg_enqueue_bf16(const void* x, int ldx, const void* w, void* out, int
 DG_API int dg_enqueue_dequantize(const uint8_t* codes, const uint8_t* scales, const float* factor, void* out,
                                  int out_kind, int N, int K, void* stream);
 
+/* Activation quantizer, FP8 per row: q [M][K] E4M3 bytes (rows ldq bytes apart) and scale [M] FP32 from x [M][K] BF16
+ * (rows ldx elements apart): scale = max(amax * fp32(1 / 448), 1e-12), q = E4M3(clamp(x / scale, +-448)), IEEE
+ * division, round to nearest even; a NaN in a row makes its scale NaN. Any M >= 1 and K >= 1; rows on 16 bytes with
+ * K % 8 == 0 are read from HBM once (staged in shared memory), others twice through L2. Replaces
+ * enqueue_quantize_fp8_rows of the reference's mma-rows package (mma_rows_cuda/mma_rows.h:109, mma_rows.cu:320-327,
+ * kernel :15-90), bit for bit. No allocation, no host synchronisation. */
+DG_API int dg_enqueue_quantize_fp8_rows(const void* x, long long ldx, int M, int K, uint8_t* q, long long ldq,
+                                        float* scale, void* stream);
+
+/* Activation quantizer, NVFP4: codes [M][K / 2] (element 2i in the low nibble of byte i, on 8 bytes) and E4M3 block
+ * scales in cuBLASLt's 128 x 4 tiled layout of [M][K / 16] (rows padded to 128, blocks to 4, the padding written as
+ * zero; on 4 bytes) from x [M][K] BF16 (rows on 16 bytes, ldx % 8 == 0), K % 16 == 0, under input scale g =
+ * input_scale with input_rcp = 1 / g: per 16 values s = E4M3(min((amax * fp32(1 / 6)) * g, 448)),
+ * d = max(e4m3(s) * input_rcp, 1e-30), code = E2M1(x / d) nearest with ties to the even code, saturating at 6, all
+ * codes 0 where e4m3(s) is not > 0. Replaces enqueue_quantize_nvfp4 (mma_rows.h:111, mma_rows.cu:329-338, kernel
+ * :117-140, arithmetic tile_parts.cuh:57-64 and :309-331), bit for bit. No allocation, no host synchronisation. */
+DG_API int dg_enqueue_quantize_nvfp4(const void* x, long long ldx, int M, int K, float input_scale, float input_rcp,
+                                     uint8_t* codes, uint8_t* blocked_scales, void* stream);
+
 /* 1 when the current device runs this build's hardware E2M1 conversion (cvt.rn.f16x2.e2m1x2; always, on the sm_100a
  * target this library is built for), -1 when the current device cannot run the library. Replaces hardware_decode
  * (decode_gemv.h:43, decode_gemv.cu:419-427); unlike it, allocates nothing and launches nothing. */

@@ -1,10 +1,12 @@
 """TEST INFRASTRUCTURE ONLY. Builds oracle/_ref/libdecode_gemv_ref.so: the reference's own CUDA source
 (decode-gemv/decode_gemv_cuda/decode_gemv.cu, two files, no build system) compiled for sm_100a from where it lies in
-the reference checkout, plus oracle/ref_shim.cu; and oracle/_ref/ref_host_check, a small program over the reference's
-header-only C++ host oracle (see build_host_check). No reference source is copied; only binaries land in oracle/_ref/
-(git-ignored, shipped to the GPU box). Without the checkout this is a no-op and whatever was built earlier is used.
+the reference checkout, plus oracle/ref_shim.cu; oracle/_ref/libmma_rows_ref.so, the same for the reference's
+activation quantizers (mma-rows/mma_rows_cuda/mma_rows.cu + fp4_mma.cu, plus oracle/ref_quant_shim.cu); and
+oracle/_ref/ref_host_check, a small program over the reference's header-only C++ host oracle (see build_host_check).
+No reference source is copied; only binaries land in oracle/_ref/ (git-ignored, shipped to the GPU box). Without the
+checkout this is a no-op and whatever was built earlier is used.
 
-    python -m oracle.build_ref [path/to/reference]
+    CRIT_KERNELS_REFERENCE=path/to/reference python -m oracle.build_ref      (or the path as the first argument)
 """
 import ctypes
 import os
@@ -17,14 +19,15 @@ LIB = os.path.join(OUT_DIR, "libdecode_gemv_ref.so")
 NVCC = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
 
 
-REFERENCE = os.environ.get("CRIT_KERNELS_REFERENCE", "/root/reference")   # the reference checkout
+REFERENCE = os.environ.get("CRIT_KERNELS_REFERENCE", "")   # the reference checkout; empty: use what is built
+QUANT_LIB = os.path.join(OUT_DIR, "libmma_rows_ref.so")
 
 
 def build(reference=REFERENCE, verbose=True):
     src_dir = os.path.join(reference, "decode-gemv", "decode_gemv_cuda")
     src = os.path.join(src_dir, "decode_gemv.cu")
     shim = os.path.join(HERE, "ref_shim.cu")
-    if not os.path.exists(src):
+    if not reference or not os.path.exists(src):
         return os.path.exists(LIB)
     if os.path.exists(LIB) and os.path.getmtime(LIB) > max(os.path.getmtime(src), os.path.getmtime(shim)):
         return True
@@ -38,6 +41,36 @@ def build(reference=REFERENCE, verbose=True):
     return True
 
 
+def build_quantizers(reference=REFERENCE, verbose=True):
+    """oracle/_ref/libmma_rows_ref.so: the reference's quantize_fp8_rows / quantize_nvfp4 kernels, unmodified."""
+    src_dir = os.path.join(reference, "mma-rows", "mma_rows_cuda")
+    sources = [os.path.join(src_dir, "mma_rows.cu"), os.path.join(src_dir, "fp4_mma.cu")]
+    shim = os.path.join(HERE, "ref_quant_shim.cu")
+    if not reference or not all(os.path.exists(f) for f in sources):
+        return os.path.exists(QUANT_LIB)
+    if os.path.exists(QUANT_LIB) and os.path.getmtime(QUANT_LIB) > max(os.path.getmtime(f) for f in sources + [shim]):
+        return True
+    os.makedirs(OUT_DIR, exist_ok=True)
+    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
+           "-Xcompiler", "-fvisibility=hidden", "-cudart", "static", f"-I{src_dir}"] + sources + [shim, "-o", QUANT_LIB]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+    return True
+
+
+def load_quantizers():
+    """The reference's quantizer library, or None when it was never built."""
+    if not os.path.exists(QUANT_LIB):
+        return None
+    lib = ctypes.CDLL(QUANT_LIB)
+    p, i, ll, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    lib.ref_quantize_fp8_rows.argtypes = [p, ll, i, i, p, ll, p, p]
+    lib.ref_quantize_nvfp4.argtypes = [p, ll, i, i, f, f, p, p, p]
+    lib.ref_quantize_fp8_rows.restype = lib.ref_quantize_nvfp4.restype = i
+    return lib
+
+
 HOST_CHECK = os.path.join(OUT_DIR, "ref_host_check")
 
 
@@ -47,7 +80,7 @@ def build_host_check(reference=REFERENCE, verbose=True):
     dependency. Used by tests/golden/make_golden.py only."""
     inc = os.path.join(reference, "fp8-block-rows", "tests", "order")
     src = os.path.join(HERE, "ref_host_check.cpp")
-    if not os.path.exists(os.path.join(inc, "row_fp8.h")):
+    if not reference or not os.path.exists(os.path.join(inc, "row_fp8.h")):
         return os.path.exists(HOST_CHECK)
     if os.path.exists(HOST_CHECK) and os.path.getmtime(HOST_CHECK) > os.path.getmtime(src):
         return True
@@ -74,6 +107,10 @@ def load():
 
 
 if __name__ == "__main__":
-    ok = build(sys.argv[1] if len(sys.argv) > 1 else REFERENCE)
-    build_host_check(sys.argv[1] if len(sys.argv) > 1 else REFERENCE)
+    where = sys.argv[1] if len(sys.argv) > 1 else REFERENCE
+    if not where:
+        raise SystemExit("give the reference checkout: CRIT_KERNELS_REFERENCE=<path> or the path as the argument")
+    ok = build(where)
+    build_quantizers(where)
+    build_host_check(where)
     print("built" if ok else "reference checkout not found; nothing built")

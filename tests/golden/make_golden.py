@@ -80,7 +80,9 @@ def host_oracle_vectors(root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CRIT_KERNELS_REFERENCE", "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CRIT_KERNELS_REFERENCE", "")
+    if not root:
+        raise SystemExit("give the reference checkout: CRIT_KERNELS_REFERENCE=<path> or the path as the argument")
     ref = load_reference_functions(os.path.join(root, "decode-gemv", "tests", "test_decode_gemv.py"))
     out = {"e2m1_table": ref["E2M1"].numpy()}
     # every E4M3 byte as torch decodes it (the reference decodes with view(float8_e4m3fn), :211)

@@ -346,3 +346,33 @@ def test_static_weight_prefetch_gives_the_same_bits(m):
     for f, w in zip(found, want):
         assert torch.equal(f, w)
     assert cabi.load().dg_take_status() == 0
+
+
+def test_a_wait_that_runs_out_reports_and_leaves_the_device_usable():
+    """No arrival ever comes for this counter: with the wait limit set to a millisecond the waiting kernel gives up,
+    sets status bit 2 and returns; after the counters are re-zeroed a normal gathered call is clean."""
+    import ctypes
+    from crit_kernels_b200 import cabi
+    lib = cabi.load()
+    dev = torch.device("cuda")
+    flags = torch.zeros(4, dtype=torch.int32, device=dev)
+    previous = lib.dg_set_wait_limit_ns(1_000_000)
+    try:
+        assert lib.dg_enqueue_gather_wait(ctypes.c_void_p(flags.data_ptr()), 0, 1, None) == 0
+        assert lib.dg_take_status() == 4                       # waited about 1 ms, gave up, said so
+    finally:
+        lib.dg_set_wait_limit_ns(previous)
+    assert lib.dg_reset_counters(ctypes.c_void_p(flags.data_ptr()), None) == 0
+    n, k, m = 300, 1024, 3
+    codes, scales, inverse = (t.to(dev) for t in wl.cfg_nvfp4(n, k, seed=77))
+    x = wl.activations(m, k, seed=78).to(dev)
+    want = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    h.run("nvfp4", x, (codes, scales, inverse), want)
+    got = torch.zeros(1, m, n, dtype=torch.bfloat16, device=dev)
+    ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+    assert lib.dg_enqueue_nvfp4_allgather(ptr(x), x.stride(0), 1, ptr(codes), ptr(scales), 0, ptr(inverse),
+                                          (ctypes.c_void_p * 1)(got.data_ptr()),
+                                          (ctypes.c_void_p * 1)(flags.data_ptr()), 1, 0, 0, 1, m, n, k, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got[0].view(torch.int16), want.view(torch.int16))
+    assert lib.dg_take_status() == 0

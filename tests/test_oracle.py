@@ -167,3 +167,29 @@ def test_mx_groups_match_the_reference_host_quantizer(golden):
     assert np.array_equal(codes.numpy() & 127, golden["host_mx_codes"] & 127)                 # magnitudes
     nonzero = (golden["host_mx_codes"] & 127) != 0
     assert np.array_equal((codes.numpy() & 128)[nonzero], (golden["host_mx_codes"] & 128)[nonzero])
+
+
+def test_quantizer_oracle_reproduces_the_reference_tests_quantizers():
+    """tests/golden/quantize_golden.npz holds what the reference test's own torch quantizers (mma-rows/tests/
+    test_mma_rows.py:80-104) give on its own inputs, evaluated on a B200 by tests/golden/make_quantize_golden.py."""
+    import os
+    import numpy as np
+    import torch
+    from oracle import quantize_oracle as qo
+    from oracle import decode_gemv_oracle as oc
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quantize_golden.npz"))
+    scale_in = float(g["input_scale"])
+    for tag in ("a", "c"):
+        x = torch.from_numpy(g[f"{tag}_x"]).view(torch.bfloat16)
+        q, scale = qo.fp8_rows(x)
+        assert np.array_equal(q, g[f"{tag}_q"]), tag
+        assert np.array_equal(scale.view(np.uint32), g[f"{tag}_scale"].view(np.uint32)), tag
+        codes, sbits = qo.nvfp4(x, scale_in)
+        assert np.array_equal(codes, g[f"{tag}_codes"]), tag
+        assert np.array_equal(sbits, g[f"{tag}_block_scales"]), tag
+    assert np.array_equal(qo.nvfp4_blocked(torch.from_numpy(g["a_x"]).view(torch.bfloat16), scale_in)[1], g["a_blocked"])
+    assert np.array_equal(oc.to_blocked(g["a_block_scales"]), g["a_blocked"])
+    xb = torch.from_numpy(g["b_x"]).view(torch.bfloat16)
+    for k in (1001, 20000):
+        q, scale = qo.fp8_rows(xb[:, :k])
+        assert np.array_equal(q, g[f"b_q_{k}"]) and np.array_equal(scale, g[f"b_scale_{k}"]), k

@@ -1,6 +1,7 @@
-"""The column-sharded NVFP4 stack on 2 (and 4) GPUs: the gathered outputs are bit-identical to the single-GPU outputs
-for every projection and M, eager and from the captured graph. Needs at least two GPUs (skipped otherwise); ranks are
-child processes over NCCL on 127.0.0.1."""
+"""The column-sharded NVFP4 stack on 2, 4 and 8 GPUs: the gathered outputs are bit-identical to the single-GPU outputs
+for every projection and M, eager and from the captured graph, also when the activations change from replay to replay
+(a gathered buffer that a fast rank overwrote too early would show there). Needs at least two GPUs (skipped
+otherwise); ranks are child processes over NCCL on 127.0.0.1."""
 import datetime
 import os
 
@@ -35,6 +36,21 @@ def _worker(rank, world, port, gather, results):
             run.replay()                                     # a second replay: the arrival counters were re-armed
             torch.cuda.synchronize()
             assert torch.equal(run.full["down"].permute(1, 0, 2).reshape(m, -1), want[-1])
+            # new activations before every replay, every role's output of every replay checked
+            alone = stk.StackRun(whole, m)
+            for rep in range(4):
+                g = torch.Generator().manual_seed(1000 + 17 * rep + m)
+                for role, k, _ in ROLES:
+                    fresh = torch.randn(m, k, generator=g).to(torch.bfloat16).to(dev)
+                    run.x[role].copy_(fresh)
+                    alone.x[role].copy_(fresh)
+                run.replay()
+                keep = []
+                alone.eager(keep)
+                torch.cuda.synchronize()
+                outs = run.outputs()
+                for (role, _, _), w in zip(ROLES, keep[-len(ROLES):]):
+                    assert torch.equal(outs[role].view(torch.int16), w.view(torch.int16)), (m, rep, role)
             del run          # a live graph that captured the group's collectives blocks the group's teardown
         results[rank] = "ok"
         torch.cuda.synchronize()
@@ -49,7 +65,7 @@ def _worker(rank, world, port, gather, results):
 
 
 @pytest.mark.parametrize("gather", ["fused", "fused-overlap", "nccl"])
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_stack_reproduces_the_single_gpu_bits(world, gather):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")

@@ -64,3 +64,17 @@ def test_sizes_beyond_the_built_in_counters_are_refused():
     assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(1, 63)) == 0      # the last channel works
     torch.cuda.synchronize()
     assert lib.dg_take_status() == 0
+    # signal-only slots are refused: nothing could collect their arrivals from the built-in counters
+    for slot in (2, 3):
+        assert lib.dg_enqueue_nvfp4_allgather_noalloc(_ptr(x), x.stride(0), 1, _ptr(codes), _ptr(scales), 0,
+                                                      _ptr(inverse), outs, devices, 1, 0, 5, slot, 1, m, n, k, None) == 1
+    # the rank's device must be the current one
+    other = (ctypes.c_int * 1)(torch.cuda.current_device() + 1)
+    assert lib.dg_enqueue_nvfp4_allgather_noalloc(_ptr(x), x.stride(0), 1, _ptr(codes), _ptr(scales), 0, _ptr(inverse),
+                                                  outs, other, 1, 0, 5, 0, 1, m, n, k, None) == 1
+    # a channel can be put back to zero in stream order, and works afterwards
+    assert lib.dg_reset_noalloc_channel(5, None) == 0
+    assert lib.dg_reset_noalloc_channel(64, None) == 1
+    assert lib.dg_enqueue_nvfp4_allgather_noalloc(*args(1, 5)) == 0
+    torch.cuda.synchronize()
+    assert lib.dg_take_status() == 0

@@ -16,6 +16,9 @@ SIGNATURES = {
     "dg_enqueue_nvfp4_allgather_noalloc": (_i, [_p, _i, _i, _p, _p, _i, _p, ctypes.POINTER(_p), _f, _i, _i, _i, _i, _i, _i,
                                                 _i, _i, _p]),
     "dg_enqueue_gather_wait": (_i, [_p, _i, ctypes.c_uint, _p]),
+    "dg_batch_blob_bytes": (ctypes.c_ulonglong, [_i]),
+    "dg_encode_nvfp4_batch": (_i, [_p, _i, _i, _i, _i, _i, _i, ctypes.POINTER(_p), _i, _p, _p]),
+    "dg_enqueue_batch": (_i, [_p, _p]),
     "dg_enqueue_fp8": (_i, [_p, _i, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_bf16": (_i, [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_enqueue_dequantize": (_i, [_p, _p, _p, _p, _i, _i, _i, _p]),
@@ -31,6 +34,14 @@ SIGNATURES = {
     "dg_set_wait_limit_ns": (ctypes.c_ulonglong, [ctypes.c_ulonglong]),
     "dg_version": (_i, []),
 }
+
+
+class Nvfp4BatchItem(ctypes.Structure):
+    """DgNvfp4BatchItem of include/decode_gemv_b200.h."""
+    _fields_ = [("x", _p), ("codes", _p), ("scales", _p), ("inverse", _p), ("out", _p), ("peer_out", ctypes.POINTER(_p)),
+                ("ldx", _i), ("ldo", _i), ("blocked", _i), ("N", _i), ("K", _i)]
+
+
 FMT = {"bf16": 0, "fp8": 1, "mxfp8": 2, "nvfp4": 3}
 _lib = None
 

@@ -84,6 +84,9 @@ DeviceState* device_state() {
   for (const void* const* table : kTables)
     for (int m = 0; ok && m < 16; ++m)
       ok = cudaFuncSetAttribute(table[m], cudaFuncAttributeMaxDynamicSharedMemorySize, dg::kSmemLimit) == cudaSuccess;
+  for (int m = 0; ok && m < 16; ++m)
+    ok = cudaFuncSetAttribute(dg_batch_table_nvfp4_bf16[m], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              dg::kSmemLimit) == cudaSuccess;
   if (!ok) {
     cudaGetLastError();
     st.ready.store(-1, std::memory_order_release);
@@ -109,13 +112,13 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 //                   DRAM efficiency and per-row bulk copies are issue-limited), up to four when a tile has few rows;
 //                   activations under 32 KB per stage
 //   stages          as many as fit in shared memory, at most kMaxStages
-bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem) {
+bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem, int grid = 0) {
   const FormatInfo f = kFormats[fmt];
   const int cw = dg::consumer_warps(fmt, M);
   const long long row_bits = (long long)K * 128 / f.e;   // 16 bytes per e elements
   p.row_bytes = (int)(row_bits / 8);
   p.nblk = p.row_bytes / 16;
-  ctas = sms < ceil_div(N, 4) ? sms : ceil_div(N, 4);
+  ctas = grid > 0 ? grid : sms < ceil_div(N, 4) ? sms : ceil_div(N, 4);   // grid: the launch is shared (batch)
   const int rows_per_cta = ceil_div(N, ctas);
   const int per_warp = ceil_div(rows_per_cta, cw);
   int rmax = dg::rows_max(fmt, M);
@@ -152,11 +155,11 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
 
 bool aligned(const void* ptr, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(ptr) % bytes == 0; }
 
-int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
+// Everything of a launch but the launch: plan, tensor maps, process-wide settings. `grid` > 0 fixes the CTA count.
+int prepare(int fmt, Params& p, int M, int& ctas, int& smem, int grid = 0) {
   DeviceState* st = device_state();
   if (!st) return (int)cudaErrorInvalidDevice;
-  int ctas = 0, smem = 0;
-  if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem)) return (int)cudaErrorInvalidValue;
+  if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem, grid)) return (int)cudaErrorInvalidValue;
   p.status = st->status;
   // Tensor maps for the 2-D copies of full row groups; without them every row travels as a 1-D bulk copy.
   const int cw = dg::consumer_warps(fmt, M);
@@ -168,16 +171,13 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   static const bool no_split = std::getenv("DG_NO_SPLIT_TAIL") != nullptr;   // tuning aid
   p.split_tail = M == 1 && !no_split;
-  if (unsigned long long* base = g_trace_base.load(std::memory_order_acquire)) {
-    const int index = g_trace_next.fetch_add(1, std::memory_order_relaxed);
-    if (index < g_trace_capacity.load(std::memory_order_relaxed))
-      p.trace = base + (size_t)index * DG_TRACE_CTAS * dg::kTraceSlots;
-  }
-  void* args[] = {&p};
-  const int threads = 32 * (dg::consumer_warps(fmt, M) + dg::producer_warps(fmt, M));
-  // Programmatic dependent launch: the kernel may start while the previous kernel of the stream drains (its launch,
-  // barrier set-up and, with static weights, its first weight copies overlap that tail); it waits for the previous
-  // kernel before it reads activations or scales from global memory and before it writes.
+  return 0;
+}
+
+// Programmatic dependent launch: the kernel may start while the previous kernel of the stream drains (its launch,
+// barrier set-up and, with static weights, its first weight copies overlap that tail); it waits for the previous
+// kernel before it reads activations or scales from global memory and before it writes.
+int launch_pdl(const void* kernel, void** args, int ctas, int threads, int smem, cudaStream_t stream) {
   static const bool no_pdl = std::getenv("DG_NO_PDL") != nullptr;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(ctas);
@@ -189,22 +189,31 @@ int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = no_pdl ? 0 : 1;
-  const cudaError_t e = cudaLaunchKernelExC(&config, kTables[table][M - 1], args);
+  const cudaError_t e = cudaLaunchKernelExC(&config, kernel, args);
   return (int)(e != cudaSuccess ? e : cudaGetLastError());
 }
 
-}  // namespace
+int launch(int table, int fmt, Params& p, int M, cudaStream_t stream) {
+  int ctas = 0, smem = 0;
+  if (const int code = prepare(fmt, p, M, ctas, smem)) return code;
+  if (unsigned long long* base = g_trace_base.load(std::memory_order_acquire)) {
+    const int index = g_trace_next.fetch_add(1, std::memory_order_relaxed);
+    if (index < g_trace_capacity.load(std::memory_order_relaxed))
+      p.trace = base + (size_t)index * DG_TRACE_CTAS * dg::kTraceSlots;
+  }
+  void* args[] = {&p};
+  const int threads = 32 * (dg::consumer_warps(fmt, M) + dg::producer_warps(fmt, M));
+  return launch_pdl(kTables[table][M - 1], args, ctas, threads, smem, stream);
+}
 
-extern "C" {
-
-int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales, int blocked,
-                     const float* inverse, void* out, int ldo, int out_kind, int M, int N, int K, void* stream) {
-  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return (int)cudaErrorInvalidValue;
-  if (!x || !codes || !scales || !inverse || !out || ldx % 8 || !aligned(x, 16) || !aligned(codes, 16) ||
-      !aligned(scales, 2) || !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1))
-    return (int)cudaErrorInvalidValue;
-  Params p{};
-  p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse; p.out = out; p.ldo = ldo;
+// Argument rules of the NVFP4 GEMV (dg_enqueue_nvfp4) and the fields they determine.
+bool fill_nvfp4(Params& p, const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales, int blocked,
+                const float* inverse, int out_kind, int M, int N, int K) {
+  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return false;
+  if (!x || !codes || !scales || !inverse || ldx % 8 || !aligned(x, 16) || !aligned(codes, 16) || !aligned(scales, 2) ||
+      !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1))
+    return false;
+  p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse;
   p.out_kind = out_kind == 0 ? dg::OUT_F32 : (x_is_bf16 ? dg::OUT_BF16 : dg::OUT_F16);
   p.N = N; p.K = K;
   p.scale_row_bytes = K / 16;
@@ -213,25 +222,40 @@ int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes
   // long (K a multiple of 256, base on 16 bytes); otherwise, and for the tiled layout, lanes read them directly.
   p.scale_mode = blocked ? dg::SCALES_BLOCKED
                          : (K % 256 == 0 && aligned(scales, 16)) ? dg::SCALES_STAGED : dg::SCALES_DIRECT;
+  return true;
+}
+
+// Head of an encoded batch (dg_encode_nvfp4_batch); the GEMVs' launch parameters follow at kBatchHead bytes.
+constexpr unsigned int kBatchMagic = 0x44474231u;   // "DGB1"
+constexpr size_t kBatchHead = 256;
+struct BatchHead {
+  unsigned int magic;
+  int count, M, ctas, smem, threads, device;
+  const void* device_blob;
+};
+static_assert(sizeof(BatchHead) <= kBatchHead && kBatchHead % alignof(Params) == 0, "batch head layout");
+
+}  // namespace
+
+extern "C" {
+
+int dg_enqueue_nvfp4(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales, int blocked,
+                     const float* inverse, void* out, int ldo, int out_kind, int M, int N, int K, void* stream) {
+  Params p{};
+  if (!out || !fill_nvfp4(p, x, ldx, x_is_bf16, codes, scales, blocked, inverse, out_kind, M, N, K))
+    return (int)cudaErrorInvalidValue;
+  p.out = out; p.ldo = ldo;
   return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
 }
 
 int dg_enqueue_nvfp4_allgather(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
                                int blocked, const float* inverse, void* const* peer_out, void* const* peer_flags,
                                int world, int rank, int slot, int out_kind, int M, int N, int K, void* stream) {
-  if (M < 1 || M > DG_MAX_ROWS || N < 1 || K < 32 || K % 32) return (int)cudaErrorInvalidValue;
-  if (!x || !codes || !scales || !inverse || !peer_out || !peer_flags || ldx % 8 || !aligned(x, 16) ||
-      !aligned(codes, 16) || !aligned(scales, 2) || !aligned(inverse, 4) || (out_kind != 0 && out_kind != 1) ||
-      world < 1 || world > dg::kMaxRanks || rank < 0 || rank >= world || slot < 0 || slot > 3)
-    return (int)cudaErrorInvalidValue;
   Params p{};
-  p.x = x; p.ldx = ldx; p.w = codes; p.scales = scales; p.row_scale = inverse; p.ldo = N;
-  p.out_kind = out_kind == 0 ? dg::OUT_F32 : (x_is_bf16 ? dg::OUT_BF16 : dg::OUT_F16);
-  p.N = N; p.K = K;
-  p.scale_row_bytes = K / 16;
-  p.ct = blocked ? (K / 16 + 3) / 4 : 0;
-  p.scale_mode = blocked ? dg::SCALES_BLOCKED
-                         : (K % 256 == 0 && aligned(scales, 16)) ? dg::SCALES_STAGED : dg::SCALES_DIRECT;
+  if (!peer_out || !peer_flags || world < 1 || world > dg::kMaxRanks || rank < 0 || rank >= world || slot < 0 ||
+      slot > 3 || !fill_nvfp4(p, x, ldx, x_is_bf16, codes, scales, blocked, inverse, out_kind, M, N, K))
+    return (int)cudaErrorInvalidValue;
+  p.ldo = N;
   p.world = world; p.rank = rank; p.gather_slot = slot & 1; p.gather_nowait = slot >> 1;
   for (int q = 0; q < world; ++q) {
     if (!peer_out[q] || !peer_flags[q] || !aligned(peer_flags[q], 4)) return (int)cudaErrorInvalidValue;
@@ -322,6 +346,76 @@ int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, co
   }
   return dg_enqueue_nvfp4_allgather(x, ldx, x_is_bf16, codes, scales, blocked, inverse, peer_out, flags, world, rank,
                                     slot, out_kind, M, N, K, stream);
+}
+
+unsigned long long dg_batch_blob_bytes(int count) { return count > 0 ? kBatchHead + (size_t)count * sizeof(Params) : 0; }
+
+int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf16, int out_kind, int M, int world, int rank,
+                          void* const* peer_flags, int slot, const void* device_blob, void* host_blob) {
+  if (!items || count < 1 || !device_blob || !host_blob || !aligned(device_blob, 256) || !aligned(host_blob, 8) ||
+      !x_is_bf16 || world < 0 || world > dg::kMaxRanks || (world > 0 && (rank < 0 || rank >= world || !peer_flags)) ||
+      slot < 0 || slot > 3)
+    return (int)cudaErrorInvalidValue;
+  DeviceState* st = device_state();
+  if (!st) return (int)cudaErrorInvalidDevice;
+  BatchHead head{};
+  Params* out = reinterpret_cast<Params*>(static_cast<unsigned char*>(host_blob) + kBatchHead);
+  int stage_bytes = 0;
+  for (int g = 0; g < count; ++g) {
+    const DgNvfp4BatchItem& it = items[g];
+    Params p{};
+    if (!fill_nvfp4(p, it.x, it.ldx, x_is_bf16, it.codes, it.scales, it.blocked, it.inverse, out_kind, M, it.N, it.K))
+      return (int)cudaErrorInvalidValue;
+    if (world > 0) {
+      if (!it.peer_out) return (int)cudaErrorInvalidValue;
+      p.ldo = it.N;
+      p.world = world; p.rank = rank; p.gather_slot = slot & 1; p.gather_nowait = slot >> 1;
+      for (int q = 0; q < world; ++q) {
+        if (!it.peer_out[q] || !peer_flags[q] || !aligned(peer_flags[q], 4)) return (int)cudaErrorInvalidValue;
+        p.peer_out[q] = it.peer_out[q];
+        p.peer_flag[q] = static_cast<unsigned int*>(peer_flags[q]);
+      }
+      p.out = it.peer_out[rank];
+    } else {
+      if (!it.out) return (int)cudaErrorInvalidValue;
+      p.out = it.out; p.ldo = it.ldo;
+    }
+    int ctas = 0, smem = 0;
+    // one grid for all: a CTA per SM, whatever a GEMV's size (a CTA without rows of a GEMV passes it by)
+    if (const int code = prepare(dg::FMT_NVFP4, p, M, ctas, smem, st->sms)) return code;
+    if (p.stage_bytes > stage_bytes) stage_bytes = p.stage_bytes;
+    out[g] = p;
+  }
+  // one ring for all: the largest stage any GEMV needs, as many of them as fit
+  int stages = (dg::kSmemLimit - dg::kSmemHeader) / stage_bytes;
+  if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+  if (stages < 2) return (int)cudaErrorInvalidValue;
+  for (int g = 0; g < count; ++g) {
+    out[g].stage_bytes = stage_bytes;
+    out[g].stages = stages;
+  }
+  head.magic = kBatchMagic; head.count = count; head.M = M; head.ctas = st->sms;
+  head.smem = dg::kSmemHeader + stages * stage_bytes;
+  head.threads = 32 * (dg::consumer_warps(dg::FMT_NVFP4, M) + dg::producer_warps(dg::FMT_NVFP4, M));
+  head.device_blob = device_blob;
+  cudaGetDevice(&head.device);
+  *reinterpret_cast<BatchHead*>(host_blob) = head;
+  return 0;
+}
+
+int dg_enqueue_batch(const void* host_blob, void* stream) {
+  if (!host_blob) return (int)cudaErrorInvalidValue;
+  const BatchHead head = *reinterpret_cast<const BatchHead*>(host_blob);
+  int device = -1;
+  if (head.magic != kBatchMagic || head.count < 1 || head.M < 1 || head.M > DG_MAX_ROWS ||
+      cudaGetDevice(&device) != cudaSuccess || device != head.device)
+    return (int)cudaErrorInvalidValue;
+  if (!device_state()) return (int)cudaErrorInvalidDevice;
+  const Params* items = reinterpret_cast<const Params*>(static_cast<const unsigned char*>(head.device_blob) + kBatchHead);
+  int count = head.count;
+  void* args[] = {&items, &count};
+  return launch_pdl(dg_batch_table_nvfp4_bf16[head.M - 1], args, head.ctas, head.threads, head.smem,
+                    static_cast<cudaStream_t>(stream));
 }
 
 int dg_enqueue_fp8(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const float* row_scale,

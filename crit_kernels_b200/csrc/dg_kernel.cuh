@@ -549,32 +549,35 @@ struct Producer {
     cp_async_arrive_noinc(full0 + 8u * s);
   }
 
-  __device__ __forceinline__ void run(volatile int* abort_flag) const {
+  // One GEMV's iterations. The ring position (stage s, its phase parity) is the caller's and carries on from one
+  // GEMV of a batch to the next; `first` is the kernel's first GEMV: only there the previous kernel of the stream may
+  // still be running (wait before the activations; with static weights, after the first weight copies).
+  __device__ __forceinline__ bool run(volatile int* abort_flag, int& s, uint32_t& parity, bool first) const {
     const int total = wk.ntiles * wk.nwin;
-    int it = 0, s = 0;
-    uint32_t parity = 0;
-    if (p.early_weights) {
+    int it = 0;
+    if (first && p.early_weights) {
       // The weights do not depend on the previous kernel of the stream: fill the ring with them before waiting for
-      // it; the activations (its output, typically) follow the wait.
-      const int first = min(p.stages, total);
-      for (int i = 0; i < first; ++i) weights(i, i);
+      // it; the activations (its output, typically) follow the wait. (First GEMV: the ring is empty, s = 0.)
+      const int ahead = min(p.stages, total);
+      for (int i = 0; i < ahead; ++i) weights(i, i);
       griddep_wait();
-      for (int i = 0; i < first; ++i) activations(i, i);
-      it = first;
-      if (first == p.stages) parity = 1u;
-      else s = first;
-    } else {
+      for (int i = 0; i < ahead; ++i) activations(i, i);
+      it = ahead;
+      if (ahead == p.stages) parity ^= 1u;
+      else s = ahead;
+    } else if (first) {
       griddep_wait();
     }
     for (; it < total; ++it) {
       if (!mbar_wait(empty0 + 8u * s, parity ^ 1u, abort_flag)) {
         if ((pl & 31) == 0 && p.status) atomicOr(p.status, kStatusProducerTimeout);
-        return;
+        return false;
       }
       weights(it, s);
       activations(it, s);
       if (++s == p.stages) { s = 0; parity ^= 1u; }
     }
+    return true;
   }
 };
 
@@ -1103,35 +1106,67 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
   return true;
 }
 
-// End of the consumer warps of a CTA in an all-gather launch. The CTA's rows [lo, hi) of this rank's slot are
-// complete in the local buffer; all consumer threads copy them, coalesced, into the other ranks' buffers; one thread
-// publishes the copies and counts the CTA done; the rank's last CTA tells every rank and waits, bounded, for all of
-// them.
+// All-gather epilogue, first half: the CTA's rows [lo, hi) of this rank's slot are complete in the local buffer; all
+// consumer threads copy them into the same place of every other rank's buffer: 16 bytes per store where the rows'
+// addresses allow it (every rank's buffer has the layout and alignment of this one), else element by element.
 template <int M, int CW>
-__device__ __forceinline__ void gather_finish(const Params& p, volatile int* abort_flag) {
+__device__ __forceinline__ void gather_copy(const Params& p) {
   const int tid = threadIdx.x;                       // consumer threads are 0 .. CW * 32 - 1
   asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+  if (p.world < 2) return;
   const int lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
   const int rows = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x) - lo;
+  const int esize = p.out_kind == OUT_F32 ? 4 : 2;
   const size_t slot0 = (size_t)p.rank * M * p.ldo + lo;
+  bool vector = true;                                // all buffers equally placed within 16 bytes
+  for (int q = 0; q < p.world; ++q)
+    vector &= ((reinterpret_cast<uintptr_t>(p.peer_out[q]) ^ reinterpret_cast<uintptr_t>(p.out)) & 15) == 0;
   // warp w copies activation rows w, w + CW, ...; its lanes run along the CTA's rows (consecutive addresses)
   const int lane = tid & 31, warp = tid >> 5;
   for (int m = warp; m < M; m += CW) {
-    const size_t idx0 = slot0 + (size_t)m * p.ldo;
-    for (int r = lane; r < rows; r += 32) {
-      if (p.out_kind == OUT_F32) {
-        const float v = reinterpret_cast<const float*>(p.out)[idx0 + r];
+    const size_t byte0 = (slot0 + (size_t)m * p.ldo) * esize;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.out) + byte0;
+    const int bytes = rows * esize;
+    // head up to the next 16-byte boundary, 16-byte body, tail
+    const int head = vector ? min(bytes, (int)((16 - (reinterpret_cast<uintptr_t>(src) & 15)) & 15)) : bytes;
+    const int body = (bytes - head) >> 4;
+    for (int i = lane * esize; i < head; i += 32 * esize) {
+      if (esize == 4) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(src + i);
         for (int q = 0; q < p.world; ++q)
-          if (q != p.rank) reinterpret_cast<float*>(p.peer_out[q])[idx0 + r] = v;
+          if (q != p.rank) *reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(p.peer_out[q]) + byte0 + i) = v;
       } else {
-        const uint16_t v = reinterpret_cast<const uint16_t*>(p.out)[idx0 + r];
+        const uint16_t v = *reinterpret_cast<const uint16_t*>(src + i);
         for (int q = 0; q < p.world; ++q)
-          if (q != p.rank) reinterpret_cast<uint16_t*>(p.peer_out[q])[idx0 + r] = v;
+          if (q != p.rank) *reinterpret_cast<uint16_t*>(static_cast<unsigned char*>(p.peer_out[q]) + byte0 + i) = v;
+      }
+    }
+    for (int i = lane; i < body; i += 32) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src + head + 16 * i);
+      for (int q = 0; q < p.world; ++q)
+        if (q != p.rank)
+          *reinterpret_cast<uint4*>(static_cast<unsigned char*>(p.peer_out[q]) + byte0 + head + 16 * i) = v;
+    }
+    for (int i = head + 16 * body + lane * esize; i < bytes; i += 32 * esize) {
+      if (esize == 4) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(src + i);
+        for (int q = 0; q < p.world; ++q)
+          if (q != p.rank) *reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(p.peer_out[q]) + byte0 + i) = v;
+      } else {
+        const uint16_t v = *reinterpret_cast<const uint16_t*>(src + i);
+        for (int q = 0; q < p.world; ++q)
+          if (q != p.rank) *reinterpret_cast<uint16_t*>(static_cast<unsigned char*>(p.peer_out[q]) + byte0 + i) = v;
       }
     }
   }
+}
+
+// Second half: one thread publishes the CTA's copies and counts the CTA done; the rank's last CTA sends `arrivals`
+// arrivals to every rank (one per gathered GEMV) and waits, bounded, until its own counter holds arrivals x world.
+template <int CW>
+__device__ __forceinline__ void gather_signal(const Params& p, volatile int* abort_flag, unsigned int arrivals) {
   asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
-  if (tid != 0) return;
+  if (threadIdx.x != 0) return;
   // System-scope operations cost about a microsecond each and this is the kernel's tail, so the chain is kept short:
   // fence (the CTA's peer copies), one acquire-release count per CTA, then the last CTA fences once and sends one
   // relaxed arrival per rank.
@@ -1146,9 +1181,10 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
   // round trips on eight GPUs).
   __threadfence_system();
   for (int q = 0; q < p.world; ++q)
-    asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(p.peer_flag[q] + p.gather_slot) : "memory");
+    asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p.peer_flag[q] + p.gather_slot), "r"(arrivals)
+                 : "memory");
   if (p.gather_nowait) return;
-  const unsigned int want = (unsigned int)p.world;
+  const unsigned int want = (unsigned int)p.world * arrivals;
   const unsigned long long start = global_ns();
   bool done = false;
   for (unsigned int i = 1; !done; ++i) {
@@ -1163,16 +1199,57 @@ __device__ __forceinline__ void gather_finish(const Params& p, volatile int* abo
     atomicOr(p.status, kStatusGatherTimeout);
 }
 
-template <int FMT, int M, typename XT>
-__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, 1)
-    gemv_kernel(const __grid_constant__ Params p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int RMAX = rows_max(FMT, M), CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);
-  constexpr bool SELF = PW == 0;             // no producer warps: the consumers issue the copies themselves
-  constexpr int COPY_WARPS = SELF ? CW : PW;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
-  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
+// The consumer warps' walk over one GEMV: tiles in order, each for up to RMAX rows a warp. The ring position (s,
+// parity) carries over; `fresh`: the ring is empty and unfilled (a kernel's first GEMV, or any GEMV of a kernel
+// whose consumers feed themselves, which starts after all its warps have left the previous one).
+template <int FMT, int M, typename XT, int CW, bool SELF>
+__device__ __forceinline__ bool consume_gemv(const Params& p, unsigned char* smem, uint32_t full0, uint32_t empty0,
+                                             volatile int* abort_flag, int& s, uint32_t& parity, bool first) {
+  constexpr int RMAX = rows_max(FMT, M);
+  const int warp = threadIdx.x >> 5;
+  const Walk<CW> wk(p);
+  const StageLayout<FMT, M, CW> lay(p);
+  if constexpr (SELF) {
+    // the first stages - 1 iterations, into the stages after s; with static weights, in a kernel's first GEMV, their
+    // weight copies leave before the previous kernel of the stream has completed
+    const int ahead = min(p.stages - 1, wk.ntiles * wk.nwin);
+    const bool early = first && p.early_weights;
+    if (early)
+      for (int i = 0; i < ahead; ++i)
+        self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, (s + i) % p.stages, true, false);
+    if (first) griddep_wait();
+    for (int i = 0; i < ahead; ++i)
+      self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, (s + i) % p.stages, !early, true);
+  } else if (first) {
+    griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
+  }
+  if (first && threadIdx.x == 0) trace_stamp(p.trace, TRACE_DEP);
+  int it = 0;
+  bool ok = true;
+  for (int t = 0; t < wk.ntiles && ok; ++t) {
+    int row0, rows;
+    wk.tile(t, row0, rows);
+    const int nr = rows > warp ? (rows - warp + CW - 1) / CW : 0;
+    // three rows have their own code only where tiles of odd heights are made on purpose (split tails)
+    constexpr bool THREE = M == 1 && RMAX == 4;
+    if (nr > (THREE ? 3 : 2))
+      ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
+                                                    it);
+    else if (THREE && nr > 2)
+      ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr,
+                                                               s, parity, it);
+    else if (nr > 1)
+      ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
+    else
+      ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
+  }
+  if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
+  return ok;
+}
+
+// Barriers and the abort word of a CTA; the first thread sets them up.
+template <int CW, int COPY_WARPS>
+__device__ __forceinline__ void ring_setup(const Params& p, uint32_t full0, uint32_t empty0, volatile int* abort_flag) {
   if (threadIdx.x == 0) {
     if (p.trace) {
       unsigned int sm;
@@ -1191,56 +1268,82 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
   }
   __syncthreads();
   griddep_launch_dependents();
+}
 
-  const int warp = threadIdx.x >> 5;
-  if (warp >= CW) {
+template <int FMT, int M, typename XT>
+__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, 1)
+    gemv_kernel(const __grid_constant__ Params p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);
+  constexpr bool SELF = PW == 0;             // no producer warps: the consumers issue the copies themselves
+  constexpr int COPY_WARPS = SELF ? CW : PW;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
+  ring_setup<CW, COPY_WARPS>(p, full0, empty0, abort_flag);
+  int s = 0;
+  uint32_t parity = 0;
+  if ((int)(threadIdx.x >> 5) >= CW) {
     if constexpr (!SELF)
-      Producer<FMT, M, CW, COPY_WARPS>(p, smem, full0, empty0, (int)threadIdx.x - CW * 32).run(abort_flag);
+      Producer<FMT, M, CW, COPY_WARPS>(p, smem, full0, empty0, (int)threadIdx.x - CW * 32).run(abort_flag, s, parity,
+                                                                                               true);
   } else {
-    const Walk<CW> wk(p);
-    const StageLayout<FMT, M, CW> lay(p);
-    if constexpr (SELF) {
-      // the first stages - 1 iterations; with static weights their weight copies leave before the previous kernel
-      // of the stream has completed
-      const int first = min(p.stages - 1, wk.ntiles * wk.nwin);
-      if (p.early_weights)
-        for (int i = 0; i < first; ++i) self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, i, true, false);
-      griddep_wait();
-      for (int i = 0; i < first; ++i)
-        self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, i, !p.early_weights, true);
-    } else {
-      griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
-    }
-    if (threadIdx.x == 0) trace_stamp(p.trace, TRACE_DEP);
-    int s = 0, it = 0;
-    uint32_t parity = 0;
-    bool ok = true;
-    for (int t = 0; t < wk.ntiles && ok; ++t) {
-      int row0, rows;
-      wk.tile(t, row0, rows);
-      const int nr = rows > warp ? (rows - warp + CW - 1) / CW : 0;
-      // three rows have their own code only where tiles of odd heights are made on purpose (split tails)
-      constexpr bool THREE = M == 1 && RMAX == 4;
-      if (nr > (THREE ? 3 : 2))
-        ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
-                                                      it);
-      else if (THREE && nr > 2)
-        ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr,
-                                                                 s, parity, it);
-      else if (nr > 1)
-        ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
-                                                      it);
-      else
-        ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
-                                                      it);
-    }
-    if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
+    consume_gemv<FMT, M, XT, CW, SELF>(p, smem, full0, empty0, abort_flag, s, parity, true);
     if ((threadIdx.x & 31) == 0) trace_stamp(p.trace, TRACE_LAST_CONSUMED);
-    if (p.world >= 1) gather_finish<M, CW>(p, abort_flag);
+    if (p.world >= 1) {
+      gather_copy<M, CW>(p);
+      gather_signal<CW>(p, abort_flag, 1u);
+    }
   }
   if ((threadIdx.x & 31) == 0) trace_stamp(p.trace, TRACE_EXIT);
   // A wait that ran out leaves copies in flight towards this CTA's shared memory: let them land before the CTA's
   // memory is handed to the next one (bounded sleep, error path only).
+  if (*abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+}
+
+// Several independent GEMVs of one format and row count in one launch: `items` (device memory) are their launch
+// parameters, all with the same ring shape (stages, stage bytes). Every CTA walks the GEMVs in order and the ring never
+// drains between them: the copies of the next GEMV's weights are in flight while the last tiles of this one are
+// consumed, which a sequence of launches cannot do (a CTA that holds the SM's shared memory must leave before the
+// next kernel's CTA can come). With the all-gather epilogue each CTA sends a GEMV's rows to the peers as soon as it has
+// finished them and goes on; the arrivals of all GEMVs are exchanged once, at the end. For GEMVs whose inputs do not
+// depend on each other's outputs only (all activations are read after one wait for the previous kernel).
+template <int FMT, int M, typename XT>
+__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, 1)
+    gemv_batch_kernel(const Params* __restrict__ items, int count) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);
+  constexpr bool SELF = PW == 0;
+  constexpr int COPY_WARPS = SELF ? CW : PW;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 2 * kMaxStages * 8);
+  const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * kMaxStages;
+  ring_setup<CW, COPY_WARPS>(items[0], full0, empty0, abort_flag);
+  int s = 0;
+  uint32_t parity = 0;
+  if ((int)(threadIdx.x >> 5) >= CW) {
+    if constexpr (!SELF) {
+      bool ok = true;
+      for (int g = 0; g < count && ok; ++g)
+        ok = Producer<FMT, M, CW, COPY_WARPS>(items[g], smem, full0, empty0, (int)threadIdx.x - CW * 32)
+                 .run(abort_flag, s, parity, g == 0);
+    }
+  } else {
+    bool ok = true;
+    for (int g = 0; g < count && ok; ++g) {
+      const Params& p = items[g];
+      ok = consume_gemv<FMT, M, XT, CW, SELF>(p, smem, full0, empty0, abort_flag, s, parity, g == 0);
+      // the CTA's rows of this GEMV go to the peers now (and, without producer warps, every warp has left the ring
+      // before the next GEMV refills it: the copy starts with a barrier of the consumer warps)
+      if (p.world >= 1 || SELF) gather_copy<M, CW>(p);
+    }
+    if ((threadIdx.x & 31) == 0) trace_stamp(items[0].trace, TRACE_LAST_CONSUMED);
+    if (items[0].world >= 1) gather_signal<CW>(items[0], abort_flag, (unsigned int)count);
+  }
+  if ((threadIdx.x & 31) == 0) trace_stamp(items[0].trace, TRACE_EXIT);
   if (*abort_flag) {
 #pragma unroll 1
     for (int i = 0; i < 2000; ++i) __nanosleep(1000);

@@ -9,3 +9,4 @@ extern const void* const dg_table_mxfp8_bf16[16];
 extern const void* const dg_table_mxfp8_f16[16];
 extern const void* const dg_table_nvfp4_bf16[16];
 extern const void* const dg_table_nvfp4_f16[16];
+extern const void* const dg_batch_table_nvfp4_bf16[16];   // gemv_batch_kernel, NVFP4, BF16 activations

@@ -79,12 +79,13 @@ class StackRun:
         self.x = {role: t.to(dev) for role, t in self.x_host.items()}
         self.shard = {role: torch.empty(m, n // stack.world, dtype=torch.bfloat16, device=dev)
                       for role, _, n in stack.roles}
-        # Gathered buffers. A rank may start storing pass k + 1 into its peers' buffers while they still read what pass
-        # k gathered (see the reuse rule in include/decode_gemv_b200.h): with waiting gathers every call is ordered
-        # behind the peers' previous calls and one set is safe for this stack; with signal-only gathers nothing
-        # orders a fast rank's next pass behind a peer's reads, so passes alternate between two sets.
+        # Gathered buffers. A rank that has finished pass k starts storing pass k + 1 (its first layers' outputs) into
+        # its peers' buffers at once, while a peer may still be reading what pass k gathered (a copy to the host, a
+        # comparison): see the reuse rule in include/decode_gemv_b200.h. Passes therefore alternate between two sets
+        # of buffers: pass k + 2 cannot start anywhere before every rank has enqueued all of pass k + 1, which each
+        # rank does after its reads of pass k.
         fused = stack.world > 1 and stack.gather.startswith("fused")
-        sets = 2 if fused and stack.gather == "fused-overlap" else 1
+        sets = 2 if fused else 1
         self.fused_sets = [FusedGatherBuffers(stack, m) for _ in range(sets)] if fused else []
         self.passes = 0                     # passes enqueued (eager or captured): picks the set of the next one
         self.calls = 0

@@ -108,6 +108,34 @@ DG_API int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_b
  * Allocates nothing. No counterpart in the reference. */
 DG_API int dg_reset_noalloc_channel(int channel, void* stream);
 
+/* Several NVFP4 GEMVs in one launch. No counterpart in the reference. For projections whose inputs do not depend on each
+ * other's outputs (q, k and v; gate and up; a benchmark's independent calls): one persistent kernel walks the GEMVs in
+ * order and never lets its stream of weights drain between them, which back-to-back launches cannot do, and with
+ * world >= 1 every GEMV's rows go to the peers as soon as a CTA has finished them, the arrivals of all GEMVs being
+ * exchanged once at the end of the launch (same buffers, counters, slots and reuse rule as
+ * dg_enqueue_nvfp4_allgather; world = 0: no gather, results to out / ldo). Every row has the bits it gets from
+ * dg_enqueue_nvfp4. All GEMVs share x's type (BF16 only), M and out_kind.
+ *   dg_batch_blob_bytes(count)   bytes of the encoded batch
+ *   dg_encode_nvfp4_batch(...)   host only: checks the GEMVs as dg_enqueue_nvfp4 does and writes their launch
+ *                                parameters into host_blob, for a copy that will live at device_blob (device memory on
+ *                                256 bytes, of the current device). The caller copies host_blob there (once: weights
+ *                                and buffers of a decode stack do not move) and keeps host_blob for the enqueue. The
+ *                                process-wide settings (static weights, wait limit) are read here.
+ *   dg_enqueue_batch(host_blob)  launches the batch on the stream; allocates nothing, waits for nothing. */
+typedef struct DgNvfp4BatchItem {
+  const void* x;             /* [M][K] BF16, rows ldx apart */
+  const uint8_t* codes;      /* as dg_enqueue_nvfp4 */
+  const uint8_t* scales;
+  const float* inverse;
+  void* out;                 /* world = 0: [M][ldo] */
+  void* const* peer_out;     /* world >= 1: host array of `world` gathered buffers [world][M][N] */
+  int ldx, ldo, blocked, N, K;
+} DgNvfp4BatchItem;
+DG_API unsigned long long dg_batch_blob_bytes(int count);
+DG_API int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf16, int out_kind, int M, int world,
+                                 int rank, void* const* peer_flags, int slot, const void* device_blob, void* host_blob);
+DG_API int dg_enqueue_batch(const void* host_blob, void* stream);
+
 /* FP8 E4M3 W8A16. Replaces enqueue_gemv_fp8 (decode_gemv.h:34-36, decode_gemv.cu:402-417).
  * Exactly one of row_scale ([N] FP32: out = row_scale[n] * sum) and mx_scale ([N][K/32] E8M0 bytes, MXFP8:
  * each weight times 2^(e - 127)) is non-null. codes [N][K] bytes on 16 bytes, K % 16 == 0 (32 for MXFP8), K >= 16. */

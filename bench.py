@@ -329,6 +329,29 @@ def run_stack(args, dev, rank, world):
         cabi.load().dg_set_static_weights(0)
         top_kernel = trials_of(g_top.replay, min(16, len(gate)), barrier, reduce_max)
         del g_top
+        # the same passes with several GEMVs a launch (legal only because the stack's GEMVs are independent; reported
+        # beside the default, never instead of it): a layer's four, and the whole pass
+        batched = []
+        if args.gather == "fused":
+            for per_launch in (4, len(model.projections)):
+                variant = model.with_batch(per_launch)
+                entry = {"gemvs_per_launch": per_launch, "ms_per_pass": [], "bit_equal_to_default": True}
+                for m in STACK_MS:
+                    vrun = variant.capture(m)
+                    entry["ms_per_pass"].append(trials_of(vrun.replay, 1, barrier, reduce_max)["us"] / 1e3)
+                    runs[m].replay()
+                    torch.cuda.synchronize()
+                    if barrier:
+                        barrier()
+                    for role, t in vrun.outputs().items():
+                        if not torch.equal(t.view(torch.int16), runs[m].outputs()[role].view(torch.int16)):
+                            entry["bit_equal_to_default"] = False
+                    if barrier:
+                        barrier()
+                    del vrun
+                if not entry["bit_equal_to_default"]:
+                    raise RuntimeError(f"{per_launch} GEMVs a launch: outputs differ from the default path's")
+                batched.append(entry)
         # end to end: activations from pinned host memory, every role's gathered output back
         for _ in range(2):
             for m in STACK_MS:
@@ -349,7 +372,7 @@ def run_stack(args, dev, rank, world):
             "pass_bytes": full_bytes, "clocks": clocks.summary(), "top_kernel": top_kernel, "top_bytes": gate_bytes,
             "h2d": sum(runs[m].h2d_bytes for m in STACK_MS), "d2h": sum(runs[m].d2h_bytes for m in STACK_MS),
             "launches": args.steps * sum(runs[m].kernel_launches for m in STACK_MS), "gather": model.gather_kind,
-            "parity": parity, "layers": layers, "model": model, "runs": runs}
+            "parity": parity, "layers": layers, "model": model, "runs": runs, "batched": batched}
 
 
 # ----- single-GPU configurations C0-C3 -----------------------------------------------------------------------------
@@ -603,7 +626,10 @@ def main():
             "config": stack_config(world, r["layers"], args.gather), "clocks": r["clocks"],
             "e2e": {"value": r["bytes_per_step"] / r["e2e_s"] / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"]},
-            "gpu_launches": r["launches"], "roofline": roofline, "parity": r["parity"], "gather": r["gather"]}
+            "gpu_launches": r["launches"], "roofline": roofline, "parity": r["parity"], "gather": r["gather"],
+            "batched_launches": {"note": "the same passes with several GEMVs a launch (dg_enqueue_batch): legal only "
+                                         "because this workload's GEMVs do not read each other's outputs; the headline "
+                                         "numbers are the one-launch-per-GEMV chain", "modes": r["batched"]}}
     if host_us is not None:
         line["host_us_per_eager_call"] = host_us
     if world == 1:

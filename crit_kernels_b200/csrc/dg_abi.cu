@@ -387,7 +387,8 @@ int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf1
     out[g] = p;
   }
   // one ring for all: the largest stage any GEMV needs, as many of them as fit
-  int stages = (dg::kSmemLimit - dg::kSmemHeader) / stage_bytes;
+  // (behind the ring: room for one GEMV's parameters, which kernels without producer warps keep there)
+  int stages = (dg::kSmemLimit - dg::kSmemHeader - (int)sizeof(Params)) / stage_bytes;
   if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return (int)cudaErrorInvalidValue;
   for (int g = 0; g < count; ++g) {
@@ -395,7 +396,7 @@ int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf1
     out[g].stages = stages;
   }
   head.magic = kBatchMagic; head.count = count; head.M = M; head.ctas = st->sms;
-  head.smem = dg::kSmemHeader + stages * stage_bytes;
+  head.smem = dg::kSmemHeader + stages * stage_bytes + (int)sizeof(Params);
   head.threads = 32 * (dg::consumer_warps(dg::FMT_NVFP4, M) + dg::producer_warps(dg::FMT_NVFP4, M));
   head.device_blob = device_blob;
   cudaGetDevice(&head.device);

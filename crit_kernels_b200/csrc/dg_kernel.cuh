@@ -453,18 +453,22 @@ template <int FMT, int M, int CW, int PW>
 struct Producer {
   static constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8, PL = 32 * PW;
   const Params& p;
+  const Params& maps;   // where the tensor maps are read from: kernel parameter or global memory, never shared memory
+                        // (p itself, unless p is a copy the CTA keeps in shared memory)
   const Walk<CW> wk;
   const StageLayout<FMT, M, CW> lay;
   const uint32_t ring, full0, empty0;
   const bool staged;
   const int pl;
 
-  __device__ __forceinline__ Producer(const Params& p_, unsigned char* smem, uint32_t full0_, uint32_t empty0_, int pl_)
-      : p(p_), wk(p_), lay(p_), ring(smem_addr(smem) + kSmemHeader), full0(full0_), empty0(empty0_),
+  __device__ __forceinline__ Producer(const Params& p_, const Params& maps_, unsigned char* smem, uint32_t full0_,
+                                      uint32_t empty0_, int pl_)
+      : p(p_), maps(maps_), wk(p_), lay(p_), ring(smem_addr(smem) + kSmemHeader), full0(full0_), empty0(empty0_),
         staged(SCB != 0 && p_.scale_mode == SCALES_STAGED), pl(pl_) {}
-  __device__ __forceinline__ Producer(const Params& p_, const Walk<CW>& wk_, const StageLayout<FMT, M, CW>& lay_,
-                                      unsigned char* smem, uint32_t full0_, uint32_t empty0_, int pl_)
-      : p(p_), wk(wk_), lay(lay_), ring(smem_addr(smem) + kSmemHeader), full0(full0_), empty0(empty0_),
+  __device__ __forceinline__ Producer(const Params& p_, const Params& maps_, const Walk<CW>& wk_,
+                                      const StageLayout<FMT, M, CW>& lay_, unsigned char* smem, uint32_t full0_,
+                                      uint32_t empty0_, int pl_)
+      : p(p_), maps(maps_), wk(wk_), lay(lay_), ring(smem_addr(smem) + kSmemHeader), full0(full0_), empty0(empty0_),
         staged(SCB != 0 && p_.scale_mode == SCALES_STAGED), pl(pl_) {}
 
   // Weight (and scale) copies of iteration `it` (tile it / nwin, window it % nwin) into stage s.
@@ -487,9 +491,9 @@ struct Producer {
       mbar_arrive_expect_tx(full, (uint32_t)box_rows * (uint32_t)(lay.w_row + (staged ? lay.sc_row : 0)) +
                                       (uint32_t)(rows - box_rows) * (uint32_t)(wbytes + scbytes));
     if (pl < boxes) {
-      tensor_g2s(stage + pl * CW * lay.w_row, &p.tmap_w, byte0 >> 3, row0 + pl * CW, full);
+      tensor_g2s(stage + pl * CW * lay.w_row, &maps.tmap_w, byte0 >> 3, row0 + pl * CW, full);
       if (staged)
-        tensor_g2s(stage + lay.sc_off + pl * lay.sc_group, &p.tmap_sc, (win * lay.sc_row) >> 3, row0 + pl * CW, full);
+        tensor_g2s(stage + lay.sc_off + pl * lay.sc_group, &maps.tmap_sc, (win * lay.sc_row) >> 3, row0 + pl * CW, full);
     }
     for (int r = box_rows + pl; r < rows; r += PL) {
       const size_t n = (size_t)(row0 + r);
@@ -970,18 +974,20 @@ template <> struct Chains<true> {
 // it + stages - 1: nobody waits for the slowest warp of the iteration just finished, and the ring runs one stage
 // short of its depth. All threads share the activation copies; the warps take turns with the weight copies.
 template <int FMT, int M, int CW>
-__device__ __forceinline__ void self_fill(const Params& p, const Walk<CW>& wk, const StageLayout<FMT, M, CW>& lay,
+__device__ __forceinline__ void self_fill(const Params& p, const Params& maps, const Walk<CW>& wk,
+                                          const StageLayout<FMT, M, CW>& lay,
                                           unsigned char* smem, uint32_t full0, uint32_t empty0, int it, int s,
                                           bool with_weights, bool with_activations) {
   const int warp = threadIdx.x >> 5;
   if (with_weights && warp == it % CW)
-    Producer<FMT, M, CW, 1>(p, wk, lay, smem, full0, empty0, (int)(threadIdx.x & 31)).weights(it, s);
+    Producer<FMT, M, CW, 1>(p, maps, wk, lay, smem, full0, empty0, (int)(threadIdx.x & 31)).weights(it, s);
   if (with_activations)
-    Producer<FMT, M, CW, CW>(p, wk, lay, smem, full0, empty0, (int)threadIdx.x).activations_shared(it, s);
+    Producer<FMT, M, CW, CW>(p, maps, wk, lay, smem, full0, empty0, (int)threadIdx.x).activations_shared(it, s);
 }
 
 template <int FMT, int M, int R, typename XT, int CW, bool SELF>
-__device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk, const StageLayout<FMT, M, CW>& lay,
+__device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps, const Walk<CW>& wk,
+                                             const StageLayout<FMT, M, CW>& lay,
                                              unsigned char* smem, uint32_t full0, uint32_t empty0,
                                              volatile int* abort_flag, int row0, int nr, int& s, uint32_t& parity,
                                              int& it) {
@@ -1070,7 +1076,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Walk<CW>& wk
       if (next < wk.ntiles * wk.nwin) {
         const int sp = s == 0 ? p.stages - 1 : s - 1;   // stage of iteration it - 1 (never used yet when it = 0)
         if (it > 0 && !mbar_wait(empty0 + 8u * sp, s == 0 ? parity ^ 1u : parity, abort_flag)) return false;
-        self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, next, sp, true, true);
+        self_fill<FMT, M, CW>(p, maps, wk, lay, smem, full0, empty0, next, sp, true, true);
       }
     }
     ++it;
@@ -1203,8 +1209,9 @@ __device__ __forceinline__ void gather_signal(const Params& p, volatile int* abo
 // parity) carries over; `fresh`: the ring is empty and unfilled (a kernel's first GEMV, or any GEMV of a kernel
 // whose consumers feed themselves, which starts after all its warps have left the previous one).
 template <int FMT, int M, typename XT, int CW, bool SELF>
-__device__ __forceinline__ bool consume_gemv(const Params& p, unsigned char* smem, uint32_t full0, uint32_t empty0,
-                                             volatile int* abort_flag, int& s, uint32_t& parity, bool first) {
+__device__ __forceinline__ bool consume_gemv(const Params& p, const Params& maps, unsigned char* smem, uint32_t full0,
+                                             uint32_t empty0, volatile int* abort_flag, int& s, uint32_t& parity,
+                                             bool first) {
   constexpr int RMAX = rows_max(FMT, M);
   const int warp = threadIdx.x >> 5;
   const Walk<CW> wk(p);
@@ -1216,10 +1223,10 @@ __device__ __forceinline__ bool consume_gemv(const Params& p, unsigned char* sme
     const bool early = first && p.early_weights;
     if (early)
       for (int i = 0; i < ahead; ++i)
-        self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, (s + i) % p.stages, true, false);
+        self_fill<FMT, M, CW>(p, maps, wk, lay, smem, full0, empty0, i, (s + i) % p.stages, true, false);
     if (first) griddep_wait();
     for (int i = 0; i < ahead; ++i)
-      self_fill<FMT, M, CW>(p, wk, lay, smem, full0, empty0, i, (s + i) % p.stages, !early, true);
+      self_fill<FMT, M, CW>(p, maps, wk, lay, smem, full0, empty0, i, (s + i) % p.stages, !early, true);
   } else if (first) {
     griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
   }
@@ -1233,15 +1240,15 @@ __device__ __forceinline__ bool consume_gemv(const Params& p, unsigned char* sme
     // three rows have their own code only where tiles of odd heights are made on purpose (split tails)
     constexpr bool THREE = M == 1 && RMAX == 4;
     if (nr > (THREE ? 3 : 2))
-      ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
+      ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
                                                     it);
     else if (THREE && nr > 2)
-      ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr,
+      ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr,
                                                                s, parity, it);
     else if (nr > 1)
-      ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
+      ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
     else
-      ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
+      ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
   }
   if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
   return ok;
@@ -1285,10 +1292,10 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
   uint32_t parity = 0;
   if ((int)(threadIdx.x >> 5) >= CW) {
     if constexpr (!SELF)
-      Producer<FMT, M, CW, COPY_WARPS>(p, smem, full0, empty0, (int)threadIdx.x - CW * 32).run(abort_flag, s, parity,
-                                                                                               true);
+      Producer<FMT, M, CW, COPY_WARPS>(p, p, smem, full0, empty0, (int)threadIdx.x - CW * 32).run(abort_flag, s, parity,
+                                                                                                  true);
   } else {
-    consume_gemv<FMT, M, XT, CW, SELF>(p, smem, full0, empty0, abort_flag, s, parity, true);
+    consume_gemv<FMT, M, XT, CW, SELF>(p, p, smem, full0, empty0, abort_flag, s, parity, true);
     if ((threadIdx.x & 31) == 0) trace_stamp(p.trace, TRACE_LAST_CONSUMED);
     if (p.world >= 1) {
       gather_copy<M, CW>(p);
@@ -1328,14 +1335,24 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
     if constexpr (!SELF) {
       bool ok = true;
       for (int g = 0; g < count && ok; ++g)
-        ok = Producer<FMT, M, CW, COPY_WARPS>(items[g], smem, full0, empty0, (int)threadIdx.x - CW * 32)
+        ok = Producer<FMT, M, CW, COPY_WARPS>(items[g], items[g], smem, full0, empty0, (int)threadIdx.x - CW * 32)
                  .run(abort_flag, s, parity, g == 0);
     }
   } else {
     bool ok = true;
+    // Where the consumers feed themselves every warp of the CTA is on the same GEMV, and the kernels are short of
+    // registers: the GEMV's parameters are then kept in shared memory behind the ring (a read from there costs less
+    // than one from global memory; a kernel parameter would cost nothing, but a batch does not fit there).
+    Params* held = reinterpret_cast<Params*>(smem + kSmemHeader + (size_t)items[0].stages * items[0].stage_bytes);
     for (int g = 0; g < count && ok; ++g) {
-      const Params& p = items[g];
-      ok = consume_gemv<FMT, M, XT, CW, SELF>(p, smem, full0, empty0, abort_flag, s, parity, g == 0);
+      if constexpr (SELF) {
+        asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(items + g);
+        for (int i = threadIdx.x; i < (int)(sizeof(Params) / 4); i += CW * 32) reinterpret_cast<uint32_t*>(held)[i] = src[i];
+        asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+      }
+      const Params& p = SELF ? *held : items[g];
+      ok = consume_gemv<FMT, M, XT, CW, SELF>(p, items[g], smem, full0, empty0, abort_flag, s, parity, g == 0);
       // the CTA's rows of this GEMV go to the peers now (and, without producer warps, every warp has left the ring
       // before the next GEMV refills it: the copy starts with a barrier of the consumer warps)
       if (p.world >= 1 || SELF) gather_copy<M, CW>(p);

@@ -97,9 +97,51 @@ class StackRun:
                          for role, _, n in stack.roles}
         self.h2d_bytes = sum(t.numel() * 2 for t in self.x_host.values())
         self.d2h_bytes = sum(t.numel() * 2 for t in self.out_host.values())
-        self.kernel_launches = len(stack.projections)
+        self.kernel_launches = (len(stack.projections) if stack.batch <= 0
+                                else -(-len(stack.projections) // stack.batch))
         self.graphs = []
         self.replays = 0
+        self.batches = self._encode_batches() if stack.batch > 0 and dev.type == "cuda" else None
+
+    def _encode_batches(self):
+        """Per set of gathered buffers, the pass as launches of `stack.batch` GEMVs each (dg_encode_nvfp4_batch): a
+        list of (host blob, device blob) pairs; the blobs and the pointer arrays they were made from stay alive
+        here."""
+        from . import cabi
+        lib, st = cabi.load(), self.stack
+        previous = lib.dg_set_static_weights(1 if st.static_weights else 0)     # read when a batch is encoded
+        try:
+            per_set = []
+            for fused in (self.fused_sets or [None]):
+                launches = []
+                for first in range(0, len(st.projections), st.batch):
+                    group = st.projections[first:first + st.batch]
+                    items = (cabi.Nvfp4BatchItem * len(group))()
+                    for item, p in zip(items, group):
+                        x = self.x[p.role]
+                        item.x, item.ldx = x.data_ptr(), x.stride(0)
+                        item.codes, item.scales, item.inverse = p.codes.data_ptr(), p.scales.data_ptr(), p.inverse.data_ptr()
+                        item.blocked, item.N, item.K = 0, p.codes.shape[0], p.k
+                        if fused:
+                            item.peer_out = ctypes.cast(fused.out_ptrs[p.role], ctypes.POINTER(ctypes.c_void_p))
+                        else:
+                            item.out, item.ldo = self.shard[p.role].data_ptr(), self.shard[p.role].stride(0)
+                    nbytes = lib.dg_batch_blob_bytes(len(group))
+                    host = torch.zeros(nbytes, dtype=torch.uint8)
+                    device = torch.zeros(nbytes, dtype=torch.uint8, device=st.device)
+                    code = lib.dg_encode_nvfp4_batch(
+                        ctypes.cast(items, ctypes.c_void_p), len(group), 1, 1, self.m, st.world if fused else 0, st.rank,
+                        fused.flag_ptrs if fused else None, (first // st.batch) & 1, ctypes.c_void_p(device.data_ptr()),
+                        ctypes.c_void_p(host.data_ptr()))
+                    if code:
+                        raise RuntimeError(f"dg_encode_nvfp4_batch: cudaError {code}")
+                    device.copy_(host)
+                    launches.append((host, device, items))
+                per_set.append(launches)
+            torch.cuda.synchronize()
+            return per_set
+        finally:
+            lib.dg_set_static_weights(previous)
 
     @property
     def fused(self):
@@ -130,6 +172,19 @@ class StackRun:
     def _pass(self, keep):
         st = self.stack
         full = self.fused.full if self.fused else self.plain_full
+        if self.batches is not None:
+            from . import cabi
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            launches = self.batches[self.passes % len(self.batches)]
+            for index, (host, _, _) in enumerate(launches):
+                code = cabi.load().dg_enqueue_batch(ctypes.c_void_p(host.data_ptr()), stream)
+                if code:
+                    raise RuntimeError(f"dg_enqueue_batch: cudaError {code}")
+                if keep is not None:       # a test reads the outputs of this launch's GEMVs (one layer at most)
+                    for p in st.projections[index * st.batch:(index + 1) * st.batch]:
+                        keep.append(full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone() if st.world > 1
+                                    else self.shard[p.role].clone())
+            return
         for p in st.projections:
             if self.fused:
                 self._gemv_allgather(p, overlap=st.gather == "fused-overlap")
@@ -230,11 +285,16 @@ class ShardedStack:
     static_weights: bool = True
     seed: int = 0
     layers: int = 0
+    batch: int = 0              # > 0: that many consecutive GEMVs per launch (dg_enqueue_batch), legal because the
+                                # stack's GEMVs do not read each other's outputs; with gather="fused" only
 
     @property
     def gather_kind(self):
         if self.world == 1:
             return "none (1 GPU)"
+        if self.gather == "fused" and self.batch > 0:
+            return (f"fused, {self.batch} GEMVs a launch: rows stored into every rank's symmetric buffer as each GEMV "
+                    "finishes, arrivals exchanged once per launch")
         if self.gather == "fused":
             return "fused into the GEMV epilogue: peer stores into every rank's symmetric buffer + arrival counters"
         if self.gather == "fused-overlap":
@@ -248,7 +308,7 @@ class ShardedStack:
 
     @classmethod
     def random(cls, layers, roles, rank, world, device, seed=0, group=None, kernel=None, gather="fused",
-               static_weights=True):
+               static_weights=True, batch=0):
         """`layers` x `roles` projections. static_weights: the stack's weights are resident and never rewritten, so
         every GEMV of a pass may start streaming them while the kernels before it finish (dg_set_static_weights is
         switched on for the duration of each enqueued pass and restored after it). Every rank draws the same full
@@ -267,8 +327,15 @@ class ShardedStack:
                 del codes, scales, inverse
         if gather not in ("fused", "fused-overlap", "nccl"):
             raise ValueError(f"gather must be 'fused', 'fused-overlap' or 'nccl', not {gather!r}")
+        if batch > 0 and world > 1 and gather != "fused":
+            raise ValueError("batched launches carry their own all-gather: gather must be 'fused'")
         return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel(), gather,
-                   static_weights, seed, layers)
+                   static_weights, seed, layers, batch)
+
+    def with_batch(self, batch):
+        """The same shards launched `batch` GEMVs at a time (0: one launch per GEMV)."""
+        import dataclasses
+        return dataclasses.replace(self, batch=batch)
 
     @staticmethod
     def full_matrix(seed, layer, idx, role_k_n, device):

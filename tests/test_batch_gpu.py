@@ -101,3 +101,25 @@ def test_a_batch_refuses_what_single_calls_refuse():
     assert code(K=k + 16) == 1 and code(N=0) == 1 and code(m_rows=17) == 1 and code(out=None) == 1
     assert code(codes=codes.data_ptr() + 1) == 1 and code(ldx=x.stride(0) + 1) == 1
     assert lib.dg_enqueue_batch(_ptr(torch.zeros(512, dtype=torch.uint8)), None) == 1     # not an encoded batch
+
+
+def test_the_stack_in_batched_launches_reproduces_the_chain_of_single_launches():
+    from crit_kernels_b200 import stack as stk
+    dev = torch.device("cuda")
+    roles = (("qkv", 1024, 1280), ("o", 1024, 1024), ("gate_up", 1024, 7168), ("down", 3584, 1024))
+    chain = stk.ShardedStack.random(3, roles, 0, 1, dev, seed=5)
+    for per_launch in (4, 3, 12):
+        batched = chain.with_batch(per_launch)
+        for m in (1, 8, 16):
+            want = chain.run(m)
+            if per_launch <= 4:
+                got = batched.run(m)
+                assert len(got) == len(want)
+                for g, w in zip(got, want):
+                    assert torch.equal(g.view(torch.int16), w.view(torch.int16)), (per_launch, m)
+            run = batched.capture(m)
+            for _ in range(2):
+                run.replay()
+                torch.cuda.synchronize()
+                for (role, _, _), w in zip(roles, want[-4:]):
+                    assert torch.equal(run.outputs()[role].view(torch.int16), w.view(torch.int16)), (per_launch, m, role)

@@ -22,7 +22,10 @@ def _worker(rank, world, port, gather, results):
                             timeout=datetime.timedelta(seconds=90))
     try:
         from crit_kernels_b200 import stack as stk
-        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=5, gather=gather)
+        batch = 0
+        if gather.startswith("batch"):
+            gather, batch = "fused", int(gather[5:])
+        sharded = stk.ShardedStack.random(2, ROLES, rank, world, dev, seed=5, gather=gather, batch=batch)
         whole = stk.ShardedStack.random(2, ROLES, 0, 1, dev, seed=5)
         for m in (1, 8, 16):
             got, want = sharded.run(m), whole.run(m)
@@ -64,13 +67,13 @@ def _worker(rank, world, port, gather, results):
         guard.cancel()
 
 
-@pytest.mark.parametrize("gather", ["fused", "fused-overlap", "nccl"])
+@pytest.mark.parametrize("gather", ["fused", "fused-overlap", "nccl", "batch4", "batch2"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_stack_reproduces_the_single_gpu_bits(world, gather):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as manager:
         results = manager.dict()
-        mp.spawn(_worker, args=(world, 29531 + world + {"fused": 10, "fused-overlap": 20, "nccl": 0}[gather], gather, results), nprocs=world,
+        mp.spawn(_worker, args=(world, 29531 + world + {"fused": 10, "fused-overlap": 20, "nccl": 0, "batch4": 30, "batch2": 40}[gather], gather, results), nprocs=world,
                  join=True)
         assert dict(results) == {r: "ok" for r in range(world)}

@@ -184,6 +184,11 @@ class StackRun:
                     for p in st.projections[index * st.batch:(index + 1) * st.batch]:
                         keep.append(full[p.role].permute(1, 0, 2).reshape(self.m, p.n).clone() if st.world > 1
                                     else self.shard[p.role].clone())
+                    if st.world > 1:
+                        # the next launch of a faster rank would store the next layer's rows into the buffers this
+                        # rank is still reading (the reuse rule): every rank finishes reading first
+                        torch.cuda.synchronize()
+                        dist.barrier(group=st.group)
             return
         for p in st.projections:
             if self.fused:

@@ -58,6 +58,10 @@ def _worker(rank, world, port, gather, results):
         results[rank] = "ok"
         torch.cuda.synchronize()
         dist.barrier()
+    except BaseException:
+        import traceback
+        results[rank] = traceback.format_exc()       # the parent shows it: the teardown below may end the process
+        raise
     finally:
         import threading
         guard = threading.Timer(30.0, lambda: os._exit(0 if results.get(rank) == "ok" else 1))
@@ -74,6 +78,9 @@ def test_sharded_stack_reproduces_the_single_gpu_bits(world, gather):
         pytest.skip(f"needs {world} GPUs")
     with mp.Manager() as manager:
         results = manager.dict()
-        mp.spawn(_worker, args=(world, 29531 + world + {"fused": 10, "fused-overlap": 20, "nccl": 0, "batch4": 30, "batch2": 40}[gather], gather, results), nprocs=world,
-                 join=True)
+        port = 29531 + world + {"fused": 10, "fused-overlap": 20, "nccl": 0, "batch4": 30, "batch2": 40}[gather]
+        try:
+            mp.spawn(_worker, args=(world, port, gather, results), nprocs=world, join=True)
+        except Exception as error:          # a rank's own traceback says more than the spawner's
+            assert dict(results) == {r: "ok" for r in range(world)}, f"{error}"
         assert dict(results) == {r: "ok" for r in range(world)}

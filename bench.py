@@ -147,6 +147,8 @@ def trials_of(fn, per_call=1, barrier=None, reduce_max=None):
     """Median / min / max over TRIALS trials of the device time of one fn(), each trial at least TRIAL_MS long.
     per_call: GEMV calls inside one fn(). Returns microseconds per call."""
     once = time_region(fn, 1, barrier)
+    if reduce_max:
+        once = reduce_max(once)      # every rank must make the same number of calls: they hold collectives
     reps = max(1, int(TRIAL_MS / max(once, 1e-3)) + 1)
     times = []
     for _ in range(TRIALS):
@@ -366,6 +368,10 @@ def run_stack(args, dev, rank, world):
         torch.cuda.synchronize()
         e2e_s = reduce_max((time.perf_counter() - t0) / args.steps)
     parity = stack_parity(model, runs, dev, rank, world)
+    status = cabi.load().dg_take_status()
+    if status:
+        raise RuntimeError(f"a bounded wait inside a kernel ran out during the run (status word {status}): the "
+                           "timings above are not those of complete passes")
     full_bytes = layers * sum(wl.weight_bytes("nvfp4", n, k) for _, k, n in wl.STACK_ROLES)
     gate_bytes = wl.weight_bytes("nvfp4", 57344 // world, 8192)
     return {"ms_per_step": ms_step, "e2e_s": e2e_s, "per_m": per_m, "bytes_per_step": full_bytes * len(STACK_MS),

@@ -354,6 +354,22 @@ def run_stack(args, dev, rank, world):
                 if not entry["bit_equal_to_default"]:
                     raise RuntimeError(f"{per_launch} GEMVs a launch: outputs differ from the default path's")
                 batched.append(entry)
+        # one GPU: the down projection fed by SwiGLU of the layer's gate_up output, as two steps and fused
+        fusion = None
+        if world == 1:
+            fusion = {"what": "down reads bf16(SwiGLU(gate_up output)): 'unfused' = SwiGLU kernel + GEMV, 'fused' = "
+                              "dg_enqueue_nvfp4_swiglu (the GEMV's producer warps form the activations; M <= 4)",
+                      "ms_per_pass": {}, "bit_equal": True}
+            for m in STACK_MS:
+                two, one = model.with_swiglu("unfused").capture(m), model.with_swiglu("fused").capture(m)
+                fusion["ms_per_pass"][str(m)] = {"unfused": trials_of(two.replay)["us"] / 1e3,
+                                                 "fused": trials_of(one.replay)["us"] / 1e3}
+                torch.cuda.synchronize()
+                if not torch.equal(two.outputs()["down"].view(torch.int16), one.outputs()["down"].view(torch.int16)):
+                    fusion["bit_equal"] = False
+                del two, one
+            if not fusion["bit_equal"]:
+                raise RuntimeError("SwiGLU fused into the down projection gives other bits than the two-step path")
         # end to end: activations from pinned host memory, every role's gathered output back
         for _ in range(2):
             for m in STACK_MS:
@@ -378,7 +394,7 @@ def run_stack(args, dev, rank, world):
             "pass_bytes": full_bytes, "clocks": clocks.summary(), "top_kernel": top_kernel, "top_bytes": gate_bytes,
             "h2d": sum(runs[m].h2d_bytes for m in STACK_MS), "d2h": sum(runs[m].d2h_bytes for m in STACK_MS),
             "launches": args.steps * sum(runs[m].kernel_launches for m in STACK_MS), "gather": model.gather_kind,
-            "parity": parity, "layers": layers, "model": model, "runs": runs, "batched": batched}
+            "parity": parity, "layers": layers, "model": model, "runs": runs, "batched": batched, "fusion": fusion}
 
 
 # ----- single-GPU configurations C0-C3 -----------------------------------------------------------------------------
@@ -520,10 +536,42 @@ def run_case(args):
     small program that profilers capture."""
     import crit_kernels_b200
     from oracle import workloads as wl
-    fmt, m, n, kk = args.case.split(":")
-    m, n, kk = int(m), int(n), int(kk)
     dev = torch.device("cuda", 0)
     k = crit_kernels_b200.get_kernel("crit-labs/decode-gemv", version=1)
+    if args.case.split(":")[0] in ("dequant", "quant_fp8", "quant_nvfp4"):
+        # the streaming kernels either side of the GEMVs: `dequant:N:K` (NVFP4 -> BF16), `quant_fp8:M:K`,
+        # `quant_nvfp4:M:K` (BF16 rows -> FP8 per row / NVFP4), two buffers in rotation, bytes read + written
+        kind, a, b = args.case.split(":")
+        a, b = int(a), int(b)
+        g = torch.Generator(device=dev).manual_seed(5)
+        if kind == "dequant":
+            sets = []
+            for _ in range(2):
+                c, s_, i = (t.to(dev) for t in wl.cfg_nvfp4(a, b))
+                sets.append((c, s_, i, torch.empty(a, b, dtype=torch.bfloat16, device=dev)))
+            calls = [lambda t=t: k.decode(t[0], t[1], t[2], t[3]) for t in sets]
+            nbytes = a * b // 2 + a * b // 16 + 4 * a + 2 * a * b
+        else:
+            xs = [(torch.randn(a, b, device=dev, generator=g) * 3).to(torch.bfloat16) for _ in range(2)]
+            if kind == "quant_fp8":
+                outs = [(torch.empty(a, b, dtype=torch.uint8, device=dev), torch.empty(a, device=dev)) for _ in xs]
+                calls = [lambda x=x, o=o: k.quantize_fp8_rows(x, o[0], o[1]) for x, o in zip(xs, outs)]
+                nbytes = 2 * a * b + a * b + 4 * a
+            else:
+                tiled = ((a + 127) // 128) * 128 * ((b // 16 + 3) // 4) * 4
+                outs = [(torch.empty(a, b // 2, dtype=torch.uint8, device=dev),
+                         torch.empty(tiled, dtype=torch.uint8, device=dev)) for _ in xs]
+                calls = [lambda x=x, o=o: k.quantize_nvfp4(x, 300.0, o[0], o[1]) for x, o in zip(xs, outs)]
+                nbytes = 2 * a * b + a * b // 2 + tiled
+        both = lambda: [c() for c in calls]
+        for _ in range(args.warmup):
+            both()
+        ms = time_region(both, args.steps) / (2 * args.steps)
+        print(json.dumps({"case": args.case, "us": ms * 1e3, "GBps": nbytes / ms / 1e6, "bytes_read_and_written": nbytes}),
+              flush=True)
+        return
+    fmt, m, n, kk = args.case.split(":")
+    m, n, kk = int(m), int(n), int(kk)
     host = {"nvfp4": lambda: wl.cfg_nvfp4(n, kk), "fp8": lambda: wl.cfg_fp8(n, kk), "mxfp8": lambda: wl.cfg_mxfp8(n, kk),
             "bf16": lambda: (wl.cfg_bf16(n, kk),)}[fmt]()
     t = tuple(a.to(dev) for a in host)
@@ -569,7 +617,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the single-GPU configurations C0-C3")
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
                     help="run `--steps` calls of one GEMV (fmt in bf16, fp8, mxfp8, nvfp4) and exit: the small case "
-                         "profilers capture")
+                         "profilers capture; also dequant:N:K, quant_fp8:M:K, quant_nvfp4:M:K")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -638,6 +686,8 @@ def main():
                                          "numbers are the one-launch-per-GEMV chain", "modes": r["batched"]}}
     if host_us is not None:
         line["host_us_per_eager_call"] = host_us
+    if r["fusion"] is not None:
+        line["swiglu_fusion"] = r["fusion"]
     if world == 1:
         sec, nbytes, what = cpu_stack_sample(reps=2)
         line["cpu_baseline"] = {"value": nbytes / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),

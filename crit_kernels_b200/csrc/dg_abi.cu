@@ -348,6 +348,24 @@ int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, co
                                     slot, out_kind, M, N, K, stream);
 }
 
+int dg_enqueue_nvfp4_swiglu(const void* gate_up, long long ldg, int gate_is_f32, void* x_scratch, const uint8_t* codes,
+                            const uint8_t* scales, int blocked, const float* inverse, void* out, int ldo, int out_kind,
+                            int M, int N, int K, void* stream) {
+  // the activations are BF16 [M][K]; the scratch stands in for x in the argument rules and in the unfused form
+  Params p{};
+  if (!gate_up || !x_scratch || !out || ldg < 2LL * K || ldg % 8 || !aligned(gate_up, 16) ||
+      !fill_nvfp4(p, x_scratch, K, 1, codes, scales, blocked, inverse, out_kind, M, N, K))
+    return (int)cudaErrorInvalidValue;
+  p.out = out; p.ldo = ldo;
+  if (dg::producer_warps(dg::FMT_NVFP4, M) > 0) {
+    p.gate_up = gate_up; p.ldg = ldg; p.gate_is_f32 = gate_is_f32 != 0;
+    return launch(5, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
+  }
+  // kernels whose consumer warps feed themselves have no warps to spare for it: SwiGLU into the scratch, then the GEMV
+  if (const int code = dg_enqueue_swiglu(gate_up, ldg, gate_is_f32, M, K, x_scratch, K, 0, stream)) return code;
+  return launch(5, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
+}
+
 unsigned long long dg_batch_blob_bytes(int count) { return count > 0 ? kBatchHead + (size_t)count * sizeof(Params) : 0; }
 
 int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf16, int out_kind, int M, int world, int rank,

@@ -32,6 +32,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "dg_swiglu.cuh"
+
 namespace dg {
 
 enum : int { FMT_BF16 = 0, FMT_FP8 = 1, FMT_MXFP8 = 2, FMT_NVFP4 = 3 };
@@ -141,6 +143,12 @@ struct Params {
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
   int early_weights;         // 1: weight copies may be issued before the previous kernel of the stream completed
   int split_tail;            // 1: a short last tile and the tile before it are walked as two equal tiles (see Walk)
+  // Fused SwiGLU (NVFP4 kernels with producer warps): when gate_up is set, x is not read; the activations are
+  // bf16(silu(gate) * up) of gate_up [M][>= 2 K] (gate in columns [0, K), up in [K, 2 K), rows ldg elements apart,
+  // FP32 or BF16), formed by the producer warps while they fill the ring.
+  const void* gate_up;
+  long long ldg;
+  int gate_is_f32;
   unsigned long long* trace; // diagnostic (dg_set_trace): kTraceSlots time stamps per CTA, or null
   unsigned long long wait_limit_ns;   // every wait in the kernel gives up after this long (status word, then leaves)
   // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results go into slot `rank` of its own
@@ -516,6 +524,54 @@ struct Producer {
     const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
     const unsigned char* xg = reinterpret_cast<const unsigned char*>(p.x);
     constexpr int STEP_SLOTS = 32 * NQ;              // 16-byte slots of one step of one activation row (64 * E bytes)
+    if constexpr (FMT == FMT_NVFP4) {
+      if (p.gate_up) {
+        // eight activations a slot from eight (gate, up) pairs: FP32 SwiGLU, one rounding to BF16, stored where the
+        // copy would have put them; a plain arrival (release) takes the place of the copies' arrival
+        const size_t k0 = xbyte0 >> 1;
+#pragma unroll 1
+        for (int m = 0; m < M; ++m) {
+          const uint32_t dst = stage + lay.x_off + m * (64 * E);
+          for (int sl = pl; sl < slots; sl += PL) {
+            const int st = sl / STEP_SLOTS, in_step = sl - st * STEP_SLOTS;
+            const size_t k = k0 + (size_t)sl * 8;
+            float g[8], u[8];
+            if (p.gate_is_f32) {
+              const float* row = reinterpret_cast<const float*>(p.gate_up) + (size_t)m * p.ldg;
+              const float4 g0 = __ldg(reinterpret_cast<const float4*>(row + k)),
+                           g1 = __ldg(reinterpret_cast<const float4*>(row + k + 4)),
+                           u0 = __ldg(reinterpret_cast<const float4*>(row + p.K + k)),
+                           u1 = __ldg(reinterpret_cast<const float4*>(row + p.K + k + 4));
+              g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+              u[0] = u0.x; u[1] = u0.y; u[2] = u0.z; u[3] = u0.w; u[4] = u1.x; u[5] = u1.y; u[6] = u1.z; u[7] = u1.w;
+            } else {
+              const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(p.gate_up) + (size_t)m * p.ldg;
+              const uint4 gv = __ldg(reinterpret_cast<const uint4*>(row + k)),
+                          uv = __ldg(reinterpret_cast<const uint4*>(row + p.K + k));
+              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                g[2 * j] = __uint_as_float(gw[j] << 16); g[2 * j + 1] = __uint_as_float(gw[j] & 0xffff0000u);
+                u[2 * j] = __uint_as_float(uw[j] << 16); u[2 * j + 1] = __uint_as_float(uw[j] & 0xffff0000u);
+              }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 pair =
+                  __floats2bfloat162_rn(swiglu_value(g[2 * j], u[2 * j]), swiglu_value(g[2 * j + 1], u[2 * j + 1]));
+              o[j] = *reinterpret_cast<const uint32_t*>(&pair);
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + st * (M * 64 * E) +
+                                                                         swizzle_slot<NQ>(in_step) * 16),
+                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                         : "memory");
+          }
+        }
+        mbar_arrive(full);
+        return;
+      }
+    }
 #pragma unroll 1
     for (int m = 0; m < M; ++m) {
       const uint32_t dst = stage + lay.x_off + m * (64 * E);

@@ -193,6 +193,8 @@ class StackRun:
         for p in st.projections:
             if self.fused:
                 self._gemv_allgather(p, overlap=st.gather == "fused-overlap")
+            elif st.swiglu and p.role == "down":
+                self._down_from_gate_up(p)
             else:
                 st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
                 if st.world > 1:
@@ -220,6 +222,26 @@ class StackRun:
                 if code:
                     raise RuntimeError(f"dg_enqueue_gather_wait: cudaError {code}")
                 pending[slot] = 0
+
+    def _down_from_gate_up(self, p):
+        """The down projection of bf16(SwiGLU(gate_up output)) on one GPU: as two steps (stack.swiglu = "unfused":
+        the SwiGLU kernel writes the activations, the GEMV reads them) or as dg_enqueue_nvfp4_swiglu ("fused")."""
+        from . import cabi
+        st, lib = self.stack, cabi.load()
+        gate_up, x, out = self.shard["gate_up"], self.x["down"], self.shard["down"]
+        ptr = lambda t: ctypes.c_void_p(t.data_ptr())
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        if st.swiglu == "unfused":
+            code = lib.dg_enqueue_swiglu(ptr(gate_up), gate_up.stride(0), 0, self.m, p.k, ptr(x), x.stride(0), 0, stream)
+            if code:
+                raise RuntimeError(f"dg_enqueue_swiglu: cudaError {code}")
+            st.kernel.gemv(x, p.codes, p.scales, p.inverse, out)
+            return
+        code = lib.dg_enqueue_nvfp4_swiglu(ptr(gate_up), gate_up.stride(0), 0, ptr(x), ptr(p.codes), ptr(p.scales), 0,
+                                           ptr(p.inverse), ptr(out), out.stride(0), 1, self.m, p.codes.shape[0], p.k,
+                                           stream)
+        if code:
+            raise RuntimeError(f"dg_enqueue_nvfp4_swiglu: cudaError {code}")
 
     def _gemv_allgather(self, p, overlap=False):
         """The GEMV with the all-gather in its epilogue (C ABI dg_enqueue_nvfp4_allgather) on the current stream."""
@@ -290,6 +312,7 @@ class ShardedStack:
     static_weights: bool = True
     seed: int = 0
     layers: int = 0
+    swiglu: str = ""            # "unfused" / "fused" (one GPU): down reads bf16(SwiGLU(the layer's gate_up output))
     batch: int = 0              # > 0: that many consecutive GEMVs per launch (dg_enqueue_batch), legal because the
                                 # stack's GEMVs do not read each other's outputs; with gather="fused" only
 
@@ -335,7 +358,14 @@ class ShardedStack:
         if batch > 0 and world > 1 and gather != "fused":
             raise ValueError("batched launches carry their own all-gather: gather must be 'fused'")
         return cls(projections, tuple(roles), rank, world, device, group, kernel or get_kernel(), gather,
-                   static_weights, seed, layers, batch)
+                   static_weights, seed, layers, "", batch)
+
+    def with_swiglu(self, mode):
+        """The same shards with the down projection fed by SwiGLU of the gate_up output ("unfused" or "fused")."""
+        import dataclasses
+        if self.world != 1 or mode not in ("unfused", "fused"):
+            raise ValueError("SwiGLU between gate_up and down is wired for one GPU, mode 'unfused' or 'fused'")
+        return dataclasses.replace(self, swiglu=mode)
 
     def with_batch(self, batch):
         """The same shards launched `batch` GEMVs at a time (0: one launch per GEMV)."""

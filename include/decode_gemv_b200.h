@@ -108,6 +108,25 @@ DG_API int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_b
  * Allocates nothing. No counterpart in the reference. */
 DG_API int dg_reset_noalloc_channel(int channel, void* stream);
 
+/* SwiGLU between the gate_up and down projections: out[row][k] = silu(gate_up[row][k]) * gate_up[row][inter + k]
+ * (gate in columns [0, inter), up in [inter, 2 inter), rows ldg elements apart; out rows ldo apart), FP32 arithmetic
+ * in the reference's declared operations (x / (1 + exp(-x)) with its polynomial exp), inputs and outputs FP32
+ * (in_is_f32 / out_is_f32 = 1) or BF16 (0; one rounding). With FP32 in and out, contiguous, it replaces enqueue_swiglu
+ * of the reference's int-block-experts package (int_block_cuda/int_block.h:65, int_block.cu:275-282, :326-331) bit for
+ * bit. No allocation, no host synchronisation. */
+DG_API int dg_enqueue_swiglu(const void* gate_up, long long ldg, int in_is_f32, int rows, int inter, void* out,
+                             long long ldo, int out_is_f32, void* stream);
+
+/* The down projection straight from the gate_up output: out = NVFP4 GEMV of x = bf16(SwiGLU(gate_up)), x [M][K] never
+ * stored when the row count's kernel has producer warps (M <= 4 for NVFP4): they form the activations while they stage
+ * them, which saves a launch and the round trip of [M][K] through memory. For larger M the call is dg_enqueue_swiglu
+ * into x_scratch ([M][K] BF16, 16-byte aligned, caller-owned, required in both cases) followed by dg_enqueue_nvfp4:
+ * the same bits either way. gate_up [M][>= 2 K] FP32 or BF16 on 16 bytes, ldg % 8 == 0; the other arguments as
+ * dg_enqueue_nvfp4. No counterpart in the reference (it runs the two steps as separate kernels). */
+DG_API int dg_enqueue_nvfp4_swiglu(const void* gate_up, long long ldg, int gate_is_f32, void* x_scratch,
+                                   const uint8_t* codes, const uint8_t* scales, int blocked, const float* inverse,
+                                   void* out, int ldo, int out_kind, int M, int N, int K, void* stream);
+
 /* Several NVFP4 GEMVs in one launch. No counterpart in the reference. For projections whose inputs do not depend on each
  * other's outputs (q, k and v; gate and up; a benchmark's independent calls): one persistent kernel walks the GEMVs in
  * order and never lets its stream of weights drain between them, which back-to-back launches cannot do, and with

@@ -1,7 +1,8 @@
 """TEST INFRASTRUCTURE ONLY. Builds oracle/_ref/libdecode_gemv_ref.so: the reference's own CUDA source
 (decode-gemv/decode_gemv_cuda/decode_gemv.cu, two files, no build system) compiled for sm_100a from where it lies in
 the reference checkout, plus oracle/ref_shim.cu; oracle/_ref/libmma_rows_ref.so, the same for the reference's
-activation quantizers (mma-rows/mma_rows_cuda/mma_rows.cu + fp4_mma.cu, plus oracle/ref_quant_shim.cu); and
+activation quantizers (mma-rows/mma_rows_cuda/mma_rows.cu + fp4_mma.cu, plus oracle/ref_quant_shim.cu);
+oracle/_ref/libint_block_ref.so for its SwiGLU (int-block-experts/int_block_cuda/int_block.cu, oracle/ref_swiglu_shim.cu); and
 oracle/_ref/ref_host_check, a small program over the reference's header-only C++ host oracle (see build_host_check).
 No reference source is copied; only binaries land in oracle/_ref/ (git-ignored, shipped to the GPU box). Without the
 checkout this is a no-op and whatever was built earlier is used.
@@ -71,6 +72,36 @@ def load_quantizers():
     return lib
 
 
+SWIGLU_LIB = os.path.join(OUT_DIR, "libint_block_ref.so")
+
+
+def build_swiglu(reference=REFERENCE, verbose=True):
+    """oracle/_ref/libint_block_ref.so: the reference's int-block-experts kernels (one file), for its swiglu."""
+    src_dir = os.path.join(reference, "int-block-experts", "int_block_cuda")
+    src, shim = os.path.join(src_dir, "int_block.cu"), os.path.join(HERE, "ref_swiglu_shim.cu")
+    if not reference or not os.path.exists(src):
+        return os.path.exists(SWIGLU_LIB)
+    if os.path.exists(SWIGLU_LIB) and os.path.getmtime(SWIGLU_LIB) > max(os.path.getmtime(src), os.path.getmtime(shim)):
+        return True
+    os.makedirs(OUT_DIR, exist_ok=True)
+    cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
+           "-Xcompiler", "-fvisibility=hidden", "-cudart", "static", f"-I{src_dir}", src, shim, "-o", SWIGLU_LIB]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+    return True
+
+
+def load_swiglu():
+    """The reference's SwiGLU library, or None when it was never built."""
+    if not os.path.exists(SWIGLU_LIB):
+        return None
+    lib = ctypes.CDLL(SWIGLU_LIB)
+    lib.ref_swiglu.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    lib.ref_swiglu.restype = ctypes.c_int
+    return lib
+
+
 HOST_CHECK = os.path.join(OUT_DIR, "ref_host_check")
 
 
@@ -112,5 +143,6 @@ if __name__ == "__main__":
         raise SystemExit("give the reference checkout: CRIT_KERNELS_REFERENCE=<path> or the path as the argument")
     ok = build(where)
     build_quantizers(where)
+    build_swiglu(where)
     build_host_check(where)
     print("built" if ok else "reference checkout not found; nothing built")

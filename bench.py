@@ -357,8 +357,9 @@ def run_stack(args, dev, rank, world):
         # one GPU: the down projection fed by SwiGLU of the layer's gate_up output, as two steps and fused
         fusion = None
         if world == 1:
-            fusion = {"what": "down reads bf16(SwiGLU(gate_up output)): 'unfused' = SwiGLU kernel + GEMV, 'fused' = "
-                              "dg_enqueue_nvfp4_swiglu (the GEMV's producer warps form the activations; M <= 4)",
+            fusion = {"what": "each layer's down projection reads bf16(SwiGLU(gate_up sums)): 'unfused' = gate_up GEMV "
+                              "(FP32 out) + SwiGLU kernel, 'fused' = SwiGLU in the gate_up GEMV's epilogue "
+                              "(dg_enqueue_nvfp4_gate_up_swiglu); then the down GEMV in both",
                       "ms_per_pass": {}, "bit_equal": True}
             for m in STACK_MS:
                 two, one = model.with_swiglu("unfused").capture(m), model.with_swiglu("fused").capture(m)

@@ -17,7 +17,7 @@ SIGNATURES = {
                                                 _i, _i, _p]),
     "dg_enqueue_gather_wait": (_i, [_p, _i, ctypes.c_uint, _p]),
     "dg_enqueue_swiglu": (_i, [_p, ctypes.c_longlong, _i, _i, _i, _p, ctypes.c_longlong, _i, _p]),
-    "dg_enqueue_nvfp4_swiglu": (_i, [_p, ctypes.c_longlong, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
+    "dg_enqueue_nvfp4_gate_up_swiglu": (_i, [_p, _i, _i, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _p]),
     "dg_batch_blob_bytes": (ctypes.c_ulonglong, [_i]),
     "dg_encode_nvfp4_batch": (_i, [_p, _i, _i, _i, _i, _i, _i, ctypes.POINTER(_p), _i, _p, _p]),
     "dg_enqueue_batch": (_i, [_p, _p]),

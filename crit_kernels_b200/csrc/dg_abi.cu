@@ -128,6 +128,7 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   if (forced && std::sscanf(forced, "%d,%d", &force_rows, &force_steps) >= 1 && force_rows >= 1 && force_rows < rmax)
     rmax = force_rows;
   p.rows_per_warp = per_warp < rmax ? per_warp : rmax;
+  if (p.pairs) p.rows_per_warp = p.rows_per_warp >= 4 ? 4 : 2;   // gate and up rows side by side: an even count
   const int rows_cap = cw * p.rows_per_warp;
   const int w_step = rows_cap * (dg::kStepBytes + f.scb);   // sizing estimate; the exact stage size is below
   const int x_step = M * 64 * f.e;
@@ -145,11 +146,12 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   p.steps = steps;
   p.stage_bytes = (steps * (rows_cap * dg::kStepBytes + x_step) +
                    p.rows_per_warp * dg::scale_group_bytes(cw, steps, f.scb) + 127) & ~127;
-  int stages = (dg::kSmemLimit - dg::kSmemHeader) / p.stage_bytes;
+  const int behind = p.pairs ? dg::kMeetBytes : 0;   // the SwiGLU epilogue's meeting place lies behind the ring
+  int stages = (dg::kSmemLimit - dg::kSmemHeader - behind) / p.stage_bytes;
   if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return false;
   p.stages = stages;
-  smem = dg::kSmemHeader + stages * p.stage_bytes;
+  smem = dg::kSmemHeader + stages * p.stage_bytes + behind;
   return true;
 }
 
@@ -164,9 +166,10 @@ int prepare(int fmt, Params& p, int M, int& ctas, int& smem, int grid = 0) {
   // Tensor maps for the 2-D copies of full row groups; without them every row travels as a 1-D bulk copy.
   const int cw = dg::consumer_warps(fmt, M);
   const int win_bytes = p.steps * dg::kStepBytes;
-  p.use_2d = p.N >= cw && encode_rows(&p.tmap_w, p.w, p.N, p.row_bytes, cw, win_bytes);
+  const int matrix_rows = p.pairs ? 2 * p.pairs : p.N;
+  p.use_2d = matrix_rows >= cw && encode_rows(&p.tmap_w, p.w, matrix_rows, p.row_bytes, cw, win_bytes);
   if (p.use_2d && p.scale_mode == dg::SCALES_STAGED)
-    p.use_2d = encode_rows(&p.tmap_sc, p.scales, p.N, p.scale_row_bytes, cw, p.steps * kFormats[fmt].scb);
+    p.use_2d = encode_rows(&p.tmap_sc, p.scales, matrix_rows, p.scale_row_bytes, cw, p.steps * kFormats[fmt].scb);
   p.early_weights = g_static_weights.load(std::memory_order_relaxed);
   p.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   static const bool no_split = std::getenv("DG_NO_SPLIT_TAIL") != nullptr;   // tuning aid
@@ -348,22 +351,19 @@ int dg_enqueue_nvfp4_allgather_noalloc(const void* x, int ldx, int x_is_bf16, co
                                     slot, out_kind, M, N, K, stream);
 }
 
-int dg_enqueue_nvfp4_swiglu(const void* gate_up, long long ldg, int gate_is_f32, void* x_scratch, const uint8_t* codes,
-                            const uint8_t* scales, int blocked, const float* inverse, void* out, int ldo, int out_kind,
-                            int M, int N, int K, void* stream) {
-  // the activations are BF16 [M][K]; the scratch stands in for x in the argument rules and in the unfused form
+int dg_enqueue_nvfp4_gate_up_swiglu(const void* x, int ldx, int x_is_bf16, const uint8_t* codes, const uint8_t* scales,
+                                    int blocked, const float* inverse, void* out, int ldo, int out_kind, int M, int I,
+                                    int K, void* stream) {
   Params p{};
-  if (!gate_up || !x_scratch || !out || ldg < 2LL * K || ldg % 8 || !aligned(gate_up, 16) ||
-      !fill_nvfp4(p, x_scratch, K, 1, codes, scales, blocked, inverse, out_kind, M, N, K))
+  if (!out || I < 1 || I > (1 << 29) ||
+      !fill_nvfp4(p, x, ldx, x_is_bf16, codes, scales, blocked, inverse, out_kind, M, 2 * I, K))
     return (int)cudaErrorInvalidValue;
   p.out = out; p.ldo = ldo;
-  if (dg::producer_warps(dg::FMT_NVFP4, M) > 0) {
-    p.gate_up = gate_up; p.ldg = ldg; p.gate_is_f32 = gate_is_f32 != 0;
-    return launch(5, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
-  }
-  // kernels whose consumer warps feed themselves have no warps to spare for it: SwiGLU into the scratch, then the GEMV
-  if (const int code = dg_enqueue_swiglu(gate_up, ldg, gate_is_f32, M, K, x_scratch, K, 0, stream)) return code;
-  return launch(5, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
+  p.pairs = I;
+  // the tiles walk whole blocks of gate rows and up rows in turn: N counts the rows in that order
+  const int cw = dg::consumer_warps(dg::FMT_NVFP4, M);
+  p.N = 2 * ((I + cw - 1) / cw) * cw;
+  return launch(x_is_bf16 ? 5 : 6, dg::FMT_NVFP4, p, M, static_cast<cudaStream_t>(stream));
 }
 
 unsigned long long dg_batch_blob_bytes(int count) { return count > 0 ? kBatchHead + (size_t)count * sizeof(Params) : 0; }

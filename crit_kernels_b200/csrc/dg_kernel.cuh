@@ -41,6 +41,8 @@ enum : int { SCALES_NONE = 0, SCALES_STAGED = 1, SCALES_DIRECT = 2, SCALES_BLOCK
 enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2 };
 
 constexpr int kMaxStages = 12;
+constexpr int RMAX_ALL = 4;                // most rows a consumer warp holds in any kernel
+constexpr int kMeetBytes = 16 * RMAX_ALL * 16 * 4;   // SwiGLU epilogue: 16 warps x (4 rows x 16 activation rows) FP32
 constexpr int kStepBytes = 512;            // 32 lanes x 16 bytes of one weight row
 constexpr int kSmemHeader = 256;           // mbarriers + abort flag
 constexpr int kSmemLimit = 232448;         // 227 KB of dynamic shared memory per CTA on sm_100
@@ -143,12 +145,10 @@ struct Params {
   int use_2d;                // 1: tmap_w (and tmap_sc when scales are staged) are valid
   int early_weights;         // 1: weight copies may be issued before the previous kernel of the stream completed
   int split_tail;            // 1: a short last tile and the tile before it are walked as two equal tiles (see Walk)
-  // Fused SwiGLU (NVFP4 kernels with producer warps): when gate_up is set, x is not read; the activations are
-  // bf16(silu(gate) * up) of gate_up [M][>= 2 K] (gate in columns [0, K), up in [K, 2 K), rows ldg elements apart,
-  // FP32 or BF16), formed by the producer warps while they fill the ring.
-  const void* gate_up;
-  long long ldg;
-  int gate_is_f32;
+  // SwiGLU epilogue (pairs > 0): the matrix is a gate_up projection of 2 * pairs rows, gate rows [0, pairs) and up rows
+  // [pairs, 2 pairs); N counts the rows as the tiles walk them (see Walk). A warp holds row k of both halves side by
+  // side and writes out[m][k] = silu(gate) * up (FP32, one rounding) instead of the two sums: `pairs` columns.
+  int pairs;
   unsigned long long* trace; // diagnostic (dg_set_trace): kTraceSlots time stamps per CTA, or null
   unsigned long long wait_limit_ns;   // every wait in the kernel gives up after this long (status word, then leaves)
   // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results go into slot `rank` of its own
@@ -392,9 +392,20 @@ template <int CW>
 struct Walk {
   int lo, hi, tile_rows, ntiles, nwin, win_bytes;
   int split_row0, split_first;   // split tail: first row and height of the last-but-one tile (split_first = 0: none)
+  int pairs;                     // SwiGLU epilogue: rows per half of the gate_up matrix (0: an ordinary matrix)
   __device__ __forceinline__ Walk(const Params& p) {
-    lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
-    hi = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
+    pairs = p.pairs;
+    if (pairs) {
+      // The tiles walk the rows in blocks of CW: block 2 b holds gate rows [b CW, (b + 1) CW), block 2 b + 1 the up
+      // rows of the same columns, so that a warp's rows 2 j and 2 j + 1 of a tile are gate and up of one column. A CTA
+      // owns whole pairs of blocks; [lo, hi) counts rows in that order (the last pair of blocks may be short).
+      const int blocks = (pairs + CW - 1) / CW;
+      lo = 2 * CW * (int)(((long long)blocks * blockIdx.x) / gridDim.x);
+      hi = 2 * CW * (int)(((long long)blocks * (blockIdx.x + 1)) / gridDim.x);
+    } else {
+      lo = (int)(((long long)p.N * blockIdx.x) / gridDim.x);
+      hi = (int)(((long long)p.N * (blockIdx.x + 1)) / gridDim.x);
+    }
     tile_rows = CW * p.rows_per_warp;
     ntiles = (hi - lo + tile_rows - 1) / tile_rows;
     // A short last tile walks every K window for a few rows: with only `stages` windows in flight and almost no
@@ -404,14 +415,28 @@ struct Walk {
     split_first = 0;
     split_row0 = 0;
     const int rows = hi - lo, rem = rows % tile_rows;
-    if (p.split_tail && rows > tile_rows && rem > 0 && 4 * rem < tile_rows) {
+    if (p.split_tail && !pairs && rows > tile_rows && rem > 0 && 4 * rem < tile_rows) {
       split_row0 = lo + (ntiles - 2) * tile_rows;
       split_first = (tile_rows + rem + 1) / 2;
     }
     win_bytes = p.steps * kStepBytes;
     nwin = (p.row_bytes + win_bytes - 1) / win_bytes;
   }
-  // First row and height of tile t.
+  // Group g of tile t (the rows a tile's consumer warps hold as their row g): first matrix row and row count (0..CW).
+  __device__ __forceinline__ void group(int t, int g, int& row0, int& rows) const {
+    if (pairs) {
+      const int first = lo + t * tile_rows + g * CW;         // in walking order
+      const int block = first / CW, k0 = (block >> 1) * CW;
+      rows = first < hi ? max(0, min(CW, pairs - k0)) : 0;
+      row0 = (block & 1) * pairs + k0;
+    } else {
+      int tile0, tile_n;
+      tile(t, tile0, tile_n);
+      row0 = tile0 + g * CW;
+      rows = max(0, min(CW, tile_n - g * CW));
+    }
+  }
+  // First row and height of tile t (ordinary matrices).
   __device__ __forceinline__ void tile(int t, int& row0, int& rows) const {
     if (split_first && t >= ntiles - 2) {
       row0 = t == ntiles - 2 ? split_row0 : split_row0 + split_first;
@@ -486,29 +511,64 @@ struct Producer {
   // cp.async arrivals are outstanding).
   __device__ __forceinline__ void weights(int it, int s) const {
     const int t = it / wk.nwin, win = it - t * wk.nwin;
-    int row0, rows;
-    wk.tile(t, row0, rows);
     const uint32_t full = full0 + 8u * s;
     const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
     const int byte0 = win * wk.win_bytes;
     const int wbytes = min(wk.win_bytes, p.row_bytes - byte0);
     const int scbytes = staged ? (wbytes * SCB) >> 9 : 0;
-    const int boxes = p.use_2d ? rows / CW : 0;
-    const int box_rows = boxes * CW;
-    if (pl == 0)
-      mbar_arrive_expect_tx(full, (uint32_t)box_rows * (uint32_t)(lay.w_row + (staged ? lay.sc_row : 0)) +
-                                      (uint32_t)(rows - box_rows) * (uint32_t)(wbytes + scbytes));
-    if (pl < boxes) {
-      tensor_g2s(stage + pl * CW * lay.w_row, &maps.tmap_w, byte0 >> 3, row0 + pl * CW, full);
-      if (staged)
-        tensor_g2s(stage + lay.sc_off + pl * lay.sc_group, &maps.tmap_sc, (win * lay.sc_row) >> 3, row0 + pl * CW, full);
+    if (!wk.pairs) {
+      // consecutive rows: the whole groups of CW rows as boxes, issued by as many lanes at once, the rest row by row
+      int row0, rows;
+      wk.tile(t, row0, rows);
+      const int boxes = p.use_2d ? rows / CW : 0;
+      const int box_rows = boxes * CW;
+      if (pl == 0)
+        mbar_arrive_expect_tx(full, (uint32_t)box_rows * (uint32_t)(lay.w_row + (staged ? lay.sc_row : 0)) +
+                                        (uint32_t)(rows - box_rows) * (uint32_t)(wbytes + scbytes));
+      if (pl < boxes) {
+        tensor_g2s(stage + pl * CW * lay.w_row, &maps.tmap_w, byte0 >> 3, row0 + pl * CW, full);
+        if (staged)
+          tensor_g2s(stage + lay.sc_off + pl * lay.sc_group, &maps.tmap_sc, (win * lay.sc_row) >> 3, row0 + pl * CW, full);
+      }
+      for (int r = box_rows + pl; r < rows; r += PL) {
+        const size_t n = (size_t)(row0 + r);
+        bulk_g2s(stage + r * lay.w_row, p.w + n * p.row_bytes + byte0, (uint32_t)wbytes, full);
+        if (staged)
+          bulk_g2s(stage + lay.sc_off + (r / CW) * lay.sc_group + (r % CW) * lay.sc_row,
+                   p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row, (uint32_t)scbytes, full);
+      }
+      return;
     }
-    for (int r = box_rows + pl; r < rows; r += PL) {
-      const size_t n = (size_t)(row0 + r);
-      bulk_g2s(stage + r * lay.w_row, p.w + n * p.row_bytes + byte0, (uint32_t)wbytes, full);
-      if (staged)
-        bulk_g2s(stage + lay.sc_off + (r / CW) * lay.sc_group + (r % CW) * lay.sc_row,
-                 p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row, (uint32_t)scbytes, full);
+    // gate_up with the SwiGLU epilogue: groups of CW rows from the two halves in turn; a whole group is one box (one
+    // lane each, issued together), a short one goes row by row
+    uint32_t expect = 0;
+    for (int g = 0; g < p.rows_per_warp; ++g) {
+      int row0, rows;
+      wk.group(t, g, row0, rows);
+      expect += p.use_2d && rows == CW ? (uint32_t)CW * (uint32_t)(lay.w_row + (staged ? lay.sc_row : 0))
+                                       : (uint32_t)rows * (uint32_t)(wbytes + scbytes);
+    }
+    if (pl == 0) mbar_arrive_expect_tx(full, expect);
+    if (pl < p.rows_per_warp) {
+      int row0, rows;
+      wk.group(t, pl, row0, rows);
+      if (p.use_2d && rows == CW) {
+        tensor_g2s(stage + pl * CW * lay.w_row, &maps.tmap_w, byte0 >> 3, row0, full);
+        if (staged)
+          tensor_g2s(stage + lay.sc_off + pl * lay.sc_group, &maps.tmap_sc, (win * lay.sc_row) >> 3, row0, full);
+      }
+    }
+    for (int g = 0; g < p.rows_per_warp; ++g) {
+      int row0, rows;
+      wk.group(t, g, row0, rows);
+      if (rows == 0 || (p.use_2d && rows == CW)) continue;
+      for (int r = pl; r < rows; r += PL) {
+        const size_t n = (size_t)(row0 + r);
+        bulk_g2s(stage + (g * CW + r) * lay.w_row, p.w + n * p.row_bytes + byte0, (uint32_t)wbytes, full);
+        if (staged)
+          bulk_g2s(stage + lay.sc_off + g * lay.sc_group + r * lay.sc_row,
+                   p.scales + n * p.scale_row_bytes + (size_t)win * lay.sc_row, (uint32_t)scbytes, full);
+      }
     }
   }
 
@@ -524,54 +584,6 @@ struct Producer {
     const size_t xbyte0 = (size_t)(byte0 >> 4) * E * 2;
     const unsigned char* xg = reinterpret_cast<const unsigned char*>(p.x);
     constexpr int STEP_SLOTS = 32 * NQ;              // 16-byte slots of one step of one activation row (64 * E bytes)
-    if constexpr (FMT == FMT_NVFP4) {
-      if (p.gate_up) {
-        // eight activations a slot from eight (gate, up) pairs: FP32 SwiGLU, one rounding to BF16, stored where the
-        // copy would have put them; a plain arrival (release) takes the place of the copies' arrival
-        const size_t k0 = xbyte0 >> 1;
-#pragma unroll 1
-        for (int m = 0; m < M; ++m) {
-          const uint32_t dst = stage + lay.x_off + m * (64 * E);
-          for (int sl = pl; sl < slots; sl += PL) {
-            const int st = sl / STEP_SLOTS, in_step = sl - st * STEP_SLOTS;
-            const size_t k = k0 + (size_t)sl * 8;
-            float g[8], u[8];
-            if (p.gate_is_f32) {
-              const float* row = reinterpret_cast<const float*>(p.gate_up) + (size_t)m * p.ldg;
-              const float4 g0 = __ldg(reinterpret_cast<const float4*>(row + k)),
-                           g1 = __ldg(reinterpret_cast<const float4*>(row + k + 4)),
-                           u0 = __ldg(reinterpret_cast<const float4*>(row + p.K + k)),
-                           u1 = __ldg(reinterpret_cast<const float4*>(row + p.K + k + 4));
-              g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
-              u[0] = u0.x; u[1] = u0.y; u[2] = u0.z; u[3] = u0.w; u[4] = u1.x; u[5] = u1.y; u[6] = u1.z; u[7] = u1.w;
-            } else {
-              const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(p.gate_up) + (size_t)m * p.ldg;
-              const uint4 gv = __ldg(reinterpret_cast<const uint4*>(row + k)),
-                          uv = __ldg(reinterpret_cast<const uint4*>(row + p.K + k));
-              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                g[2 * j] = __uint_as_float(gw[j] << 16); g[2 * j + 1] = __uint_as_float(gw[j] & 0xffff0000u);
-                u[2 * j] = __uint_as_float(uw[j] << 16); u[2 * j + 1] = __uint_as_float(uw[j] & 0xffff0000u);
-              }
-            }
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const __nv_bfloat162 pair =
-                  __floats2bfloat162_rn(swiglu_value(g[2 * j], u[2 * j]), swiglu_value(g[2 * j + 1], u[2 * j + 1]));
-              o[j] = *reinterpret_cast<const uint32_t*>(&pair);
-            }
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst + st * (M * 64 * E) +
-                                                                         swizzle_slot<NQ>(in_step) * 16),
-                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                         : "memory");
-          }
-        }
-        mbar_arrive(full);
-        return;
-      }
-    }
 #pragma unroll 1
     for (int m = 0; m < M; ++m) {
       const uint32_t dst = stage + lay.x_off + m * (64 * E);
@@ -1045,7 +1057,7 @@ template <int FMT, int M, int R, typename XT, int CW, bool SELF>
 __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps, const Walk<CW>& wk,
                                              const StageLayout<FMT, M, CW>& lay,
                                              unsigned char* smem, uint32_t full0, uint32_t empty0,
-                                             volatile int* abort_flag, int row0, int nr, int& s, uint32_t& parity,
+                                             volatile int* abort_flag, int t, int nr, int& s, uint32_t& parity,
                                              int& it) {
   constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
   constexpr bool FEW = few_rows(FMT, M);
@@ -1069,6 +1081,21 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
   }
   const bool staged = SCB != 0 && p.scale_mode == SCALES_STAGED;
   const uint32_t ring = smem_addr(smem) + kSmemHeader;
+  int rown[R];   // matrix row of each of the warp's rows (rows it does not have alias its last real one)
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    int group0, group_n;
+    wk.group(t, min(r, max(nr, 1) - 1), group0, group_n);
+    rown[r] = group0 + warp;
+  }
+
+  // row r's matrix row for an r known only at run time, without indexing the array (it stays in registers)
+  auto row_of = [&](int r) {
+    int n = rown[0];
+#pragma unroll
+    for (int q = 1; q < R; ++q) n = r == q ? rown[q] : n;
+    return n;
+  };
 
   for (int win = 0; win < wk.nwin; ++win) {
     if (!mbar_wait(full0 + 8u * s, parity, abort_flag)) return false;
@@ -1100,7 +1127,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
             } else {
 #pragma unroll
               for (int r = 0; r < R; ++r) {
-                const int n = row0 + warp + CW * min(r, nr - 1);
+                const int n = rown[r];
                 sc[r] = e8m0_to_f32(__ldg(p.scales + (size_t)n * p.scale_row_bytes + (blk >> 1)));
               }
             }
@@ -1113,7 +1140,7 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
             } else {
 #pragma unroll
               for (int r = 0; r < R; ++r) {
-                const int n = row0 + warp + CW * min(r, nr - 1);
+                const int n = rown[r];
                 const size_t off = p.scale_mode == SCALES_BLOCKED ? tiled_scale_offset(n, blk * 2, p.ct)
                                                                    : (size_t)n * p.scale_row_bytes + blk * 2;
                 sc[r] = e4m3x2_to_f32(__ldg(reinterpret_cast<const uint16_t*>(p.scales + off)));
@@ -1148,13 +1175,35 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
     for (int m = 0; m < M; ++m) val[r * M + m] = sum2(acc[r][m]);
   float total[(V + 31) / 32];
   LaneReduce<V, 16, (V + 31) / 32>::run(val, lane, total);
+  if constexpr (FMT == FMT_NVFP4 && R % 2 == 0) {
+    if (p.pairs) {
+      // SwiGLU epilogue: the scaled sums of the warp's rows meet in the warp's corner of shared memory behind the
+      // ring; lane (j, m) then combines gate row 2 j and up row 2 j + 1 and writes one activation.
+      float* meet = reinterpret_cast<float*>(smem + kSmemHeader + (size_t)p.stages * p.stage_bytes) + warp * (RMAX_ALL * 16);
+#pragma unroll
+      for (int i = 0; i < (V + 31) / 32; ++i) {
+        const int v = lane_value<V>(lane, i);
+        if (v >= 0) meet[v] = total[i] * __ldg(p.row_scale + row_of(v / M));
+      }
+      __syncwarp();
+      if (lane < (R / 2) * M) {
+        const int j = lane / M, m = lane - j * M;
+        if (2 * j < nr) {
+          const float result = swiglu_value(meet[2 * j * M + m], meet[(2 * j + 1) * M + m]);
+          store_out(p.out, p.out_kind, (size_t)m * p.ldo + row_of(2 * j), result);
+        }
+      }
+      __syncwarp();
+      return true;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < (V + 31) / 32; ++i) {
     const int v = lane_value<V>(lane, i);
     if (v >= 0) {
       const int r = v / M, m = v - r * M;
       if (r < nr) {
-        const int n = row0 + warp + CW * r;
+        const int n = row_of(r);
         const float sum = total[i];
         const float result = p.row_scale ? sum * __ldg(p.row_scale + n) : sum;
         if (p.world < 1) {
@@ -1290,21 +1339,24 @@ __device__ __forceinline__ bool consume_gemv(const Params& p, const Params& maps
   int it = 0;
   bool ok = true;
   for (int t = 0; t < wk.ntiles && ok; ++t) {
-    int row0, rows;
-    wk.tile(t, row0, rows);
-    const int nr = rows > warp ? (rows - warp + CW - 1) / CW : 0;
+    int nr = 0;                      // rows this warp holds in the tile: one per group that reaches it
+    for (int g = 0; g < p.rows_per_warp; ++g) {
+      int group0, group_n;
+      wk.group(t, g, group0, group_n);
+      if (warp < group_n) nr = g + 1;
+    }
     // three rows have their own code only where tiles of odd heights are made on purpose (split tails)
     constexpr bool THREE = M == 1 && RMAX == 4;
     if (nr > (THREE ? 3 : 2))
-      ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity,
+      ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity,
                                                     it);
     else if (THREE && nr > 2)
-      ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr,
+      ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr,
                                                                s, parity, it);
     else if (nr > 1)
-      ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
+      ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity, it);
     else
-      ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, row0, nr, s, parity, it);
+      ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity, it);
   }
   if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
   return ok;

@@ -101,6 +101,7 @@ class StackRun:
                                 else -(-len(stack.projections) // stack.batch))
         self.graphs = []
         self.replays = 0
+        self.gate_up_f32 = None
         self.batches = self._encode_batches() if stack.batch > 0 and dev.type == "cuda" else None
 
     def _encode_batches(self):
@@ -193,8 +194,8 @@ class StackRun:
         for p in st.projections:
             if self.fused:
                 self._gemv_allgather(p, overlap=st.gather == "fused-overlap")
-            elif st.swiglu and p.role == "down":
-                self._down_from_gate_up(p)
+            elif st.swiglu and p.role == "gate_up":
+                self._gate_up_to_down(p)
             else:
                 st.kernel.gemv(self.x[p.role], p.codes, p.scales, p.inverse, self.shard[p.role])
                 if st.world > 1:
@@ -223,25 +224,28 @@ class StackRun:
                     raise RuntimeError(f"dg_enqueue_gather_wait: cudaError {code}")
                 pending[slot] = 0
 
-    def _down_from_gate_up(self, p):
-        """The down projection of bf16(SwiGLU(gate_up output)) on one GPU: as two steps (stack.swiglu = "unfused":
-        the SwiGLU kernel writes the activations, the GEMV reads them) or as dg_enqueue_nvfp4_swiglu ("fused")."""
+    def _gate_up_to_down(self, p):
+        """gate_up on one GPU with SwiGLU behind it, writing the down projection's activations x["down"] = bf16 of the
+        FP32 SwiGLU of the FP32 sums: as two launches (stack.swiglu = "unfused": the GEMV writes FP32 [M][2 I], the
+        SwiGLU kernel reads it) or as one (dg_enqueue_nvfp4_gate_up_swiglu, "fused"). Same bits either way."""
         from . import cabi
         st, lib = self.stack, cabi.load()
-        gate_up, x, out = self.shard["gate_up"], self.x["down"], self.shard["down"]
+        x, acts = self.x[p.role], self.x["down"]
         ptr = lambda t: ctypes.c_void_p(t.data_ptr())
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        inter = p.codes.shape[0] // 2
         if st.swiglu == "unfused":
-            code = lib.dg_enqueue_swiglu(ptr(gate_up), gate_up.stride(0), 0, self.m, p.k, ptr(x), x.stride(0), 0, stream)
-            if code:
-                raise RuntimeError(f"dg_enqueue_swiglu: cudaError {code}")
-            st.kernel.gemv(x, p.codes, p.scales, p.inverse, out)
-            return
-        code = lib.dg_enqueue_nvfp4_swiglu(ptr(gate_up), gate_up.stride(0), 0, ptr(x), ptr(p.codes), ptr(p.scales), 0,
-                                           ptr(p.inverse), ptr(out), out.stride(0), 1, self.m, p.codes.shape[0], p.k,
-                                           stream)
+            if self.gate_up_f32 is None:
+                self.gate_up_f32 = torch.empty(self.m, 2 * inter, dtype=torch.float32, device=st.device)
+            st.kernel.gemv(x, p.codes, p.scales, p.inverse, self.gate_up_f32)
+            code = lib.dg_enqueue_swiglu(ptr(self.gate_up_f32), 2 * inter, 1, self.m, inter, ptr(acts), acts.stride(0), 0,
+                                         stream)
+        else:
+            code = lib.dg_enqueue_nvfp4_gate_up_swiglu(ptr(x), x.stride(0), 1, ptr(p.codes), ptr(p.scales), 0,
+                                                       ptr(p.inverse), ptr(acts), acts.stride(0), 1, self.m, inter, p.k,
+                                                       stream)
         if code:
-            raise RuntimeError(f"dg_enqueue_nvfp4_swiglu: cudaError {code}")
+            raise RuntimeError(f"gate_up + SwiGLU ({st.swiglu}): cudaError {code}")
 
     def _gemv_allgather(self, p, overlap=False):
         """The GEMV with the all-gather in its epilogue (C ABI dg_enqueue_nvfp4_allgather) on the current stream."""
@@ -312,7 +316,7 @@ class ShardedStack:
     static_weights: bool = True
     seed: int = 0
     layers: int = 0
-    swiglu: str = ""            # "unfused" / "fused" (one GPU): down reads bf16(SwiGLU(the layer's gate_up output))
+    swiglu: str = ""            # "unfused" / "fused" (one GPU): gate_up's SwiGLU feeds the layer's down projection
     batch: int = 0              # > 0: that many consecutive GEMVs per launch (dg_enqueue_batch), legal because the
                                 # stack's GEMVs do not read each other's outputs; with gather="fused" only
 
@@ -361,7 +365,8 @@ class ShardedStack:
                    static_weights, seed, layers, "", batch)
 
     def with_swiglu(self, mode):
-        """The same shards with the down projection fed by SwiGLU of the gate_up output ("unfused" or "fused")."""
+        """The same shards with each layer's down projection fed by the SwiGLU of its gate_up projection, as two
+        launches ("unfused") or in gate_up's epilogue ("fused")."""
         import dataclasses
         if self.world != 1 or mode not in ("unfused", "fused"):
             raise ValueError("SwiGLU between gate_up and down is wired for one GPU, mode 'unfused' or 'fused'")

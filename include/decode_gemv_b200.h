@@ -117,15 +117,16 @@ DG_API int dg_reset_noalloc_channel(int channel, void* stream);
 DG_API int dg_enqueue_swiglu(const void* gate_up, long long ldg, int in_is_f32, int rows, int inter, void* out,
                              long long ldo, int out_is_f32, void* stream);
 
-/* The down projection straight from the gate_up output: out = NVFP4 GEMV of x = bf16(SwiGLU(gate_up)), x [M][K] never
- * stored when the row count's kernel has producer warps (M <= 4 for NVFP4): they form the activations while they stage
- * them, which saves a launch and the round trip of [M][K] through memory. For larger M the call is dg_enqueue_swiglu
- * into x_scratch ([M][K] BF16, 16-byte aligned, caller-owned, required in both cases) followed by dg_enqueue_nvfp4:
- * the same bits either way. gate_up [M][>= 2 K] FP32 or BF16 on 16 bytes, ldg % 8 == 0; the other arguments as
- * dg_enqueue_nvfp4. No counterpart in the reference (it runs the two steps as separate kernels). */
-DG_API int dg_enqueue_nvfp4_swiglu(const void* gate_up, long long ldg, int gate_is_f32, void* x_scratch,
-                                   const uint8_t* codes, const uint8_t* scales, int blocked, const float* inverse,
-                                   void* out, int ldo, int out_kind, int M, int N, int K, void* stream);
+/* The gate_up projection with SwiGLU in its epilogue: the NVFP4 matrix holds 2 I rows, gate rows [0, I) and up rows
+ * [I, 2 I) (codes [2 I][K / 2], scales, inverse [2 I] as dg_enqueue_nvfp4), and out [M][ldo] receives the I activations
+ * of the down projection, out[m][k] = silu(g) * u with g, u the two finished FP32 sums times their inverse scales, in the
+ * arithmetic of dg_enqueue_swiglu, rounded once to out's type (out_kind 0 FP32, 1 x's type). A warp holds row k of both
+ * halves side by side, so nothing but the activations is written: no [M][2 I] intermediate, no second launch. The bits
+ * are those of dg_enqueue_nvfp4 with FP32 output followed by dg_enqueue_swiglu. No counterpart in the reference (it
+ * runs the steps as separate kernels: int_block.cu:275-282 is its SwiGLU). */
+DG_API int dg_enqueue_nvfp4_gate_up_swiglu(const void* x, int ldx, int x_is_bf16, const uint8_t* codes,
+                                           const uint8_t* scales, int blocked, const float* inverse, void* out, int ldo,
+                                           int out_kind, int M, int I, int K, void* stream);
 
 /* Several NVFP4 GEMVs in one launch. No counterpart in the reference. For projections whose inputs do not depend on each
  * other's outputs (q, k and v; gate and up; a benchmark's independent calls): one persistent kernel walks the GEMVs in

@@ -56,34 +56,36 @@ def test_swiglu_matches_the_oracle_and_the_reference_kernel(rows, inter):
     assert lib.dg_enqueue_swiglu(_ptr(gu), inter, 1, rows, inter, _ptr(out), inter, 1, None) == 1     # rows too close
 
 
-@pytest.mark.parametrize("gate_f32", [True, False])
-@pytest.mark.parametrize("n,k", [(520, 2048), (96, 256), (1024, 3584)])
-def test_the_down_projection_forms_its_activations_with_the_bits_of_the_two_step_path(n, k, gate_f32):
+@pytest.mark.parametrize("inter,k", [(520, 2048), (96, 256), (7168, 1024), (1001, 512), (5, 32)])
+def test_gate_up_with_the_swiglu_epilogue_gives_the_bits_of_the_two_step_path(inter, k):
     dev = torch.device("cuda")
     lib = cabi.load()
-    codes, scales, inverse = (t.to(dev) for t in wl.cfg_nvfp4(n, k, seed=60))
-    host_values = oc.values_of("nvfp4", wl.cfg_nvfp4(n, k, seed=60))
+    host = wl.cfg_nvfp4(2 * inter, k, seed=60)
+    codes, scales, inverse = (t.to(dev) for t in host)
+    inverse = (inverse * (torch.rand(2 * inter, device=dev) + 0.5)).contiguous()      # scales that differ per row
     for m in range(1, 17):
-        gu = gate_up_values(m, k, 70 + m).to(dev)
-        gu = gu if gate_f32 else gu.to(torch.bfloat16)
-        x = torch.empty(m, k, dtype=torch.bfloat16, device=dev)
-        assert lib.dg_enqueue_swiglu(_ptr(gu), 2 * k, int(gate_f32), m, k, _ptr(x), k, 0, None) == 0
-        want = torch.empty(m, n, device=dev)
-        h.run("nvfp4", x, (codes, scales, inverse), want)
-        got = torch.full((m, n), -1.0, device=dev)
-        scratch = torch.zeros(m, k, dtype=torch.bfloat16, device=dev)
-        code = lib.dg_enqueue_nvfp4_swiglu(_ptr(gu), 2 * k, int(gate_f32), _ptr(scratch), _ptr(codes), _ptr(scales), 0,
-                                           _ptr(inverse), _ptr(got), n, 0, m, n, k, None)
-        assert code == 0, code
-        torch.cuda.synchronize()
-        assert torch.equal(got.view(torch.int32), want.view(torch.int32)), m
-        assert oc.within_fp32_bound(got, x.cpu(), host_values), m          # and the product is the oracle's
+        x = wl.activations(m, k, seed=70 + m).to(dev)
+        sums = torch.empty(m, 2 * inter, device=dev)
+        h.run("nvfp4", x, (codes, scales, inverse), sums)                             # FP32 gate and up sums
+        for out_dtype, kind in ((torch.bfloat16, 1), (torch.float32, 0)):
+            want = torch.empty(m, inter, dtype=out_dtype, device=dev)
+            assert lib.dg_enqueue_swiglu(_ptr(sums), 2 * inter, 1, m, inter, _ptr(want), inter,
+                                         int(out_dtype == torch.float32), None) == 0
+            got = torch.full((m, inter + 8), -1.0, dtype=out_dtype, device=dev)       # padded rows: nothing beside them
+            code = lib.dg_enqueue_nvfp4_gate_up_swiglu(_ptr(x), x.stride(0), 1, _ptr(codes), _ptr(scales), 0,
+                                                       _ptr(inverse), _ptr(got), inter + 8, kind, m, inter, k, None)
+            assert code == 0, code
+            torch.cuda.synchronize()
+            assert torch.equal(got[:, :inter].contiguous().view(torch.int16 if kind else torch.int32),
+                               want.view(torch.int16 if kind else torch.int32)), (m, out_dtype)
+            assert bool((got[:, inter:] == -1.0).all())
     assert lib.dg_take_status() == 0
-    # refusals: no scratch, gate_up rows too close or unaligned
-    gu = gate_up_values(2, k, 1).to(dev)
-    out = torch.empty(2, n, device=dev)
-    scratch = torch.zeros(2, k, dtype=torch.bfloat16, device=dev)
-    args = lambda g, ld, s: (_ptr(g), ld, 1, s, _ptr(codes), _ptr(scales), 0, _ptr(inverse), _ptr(out), n, 0, 2, n, k, None)
-    assert lib.dg_enqueue_nvfp4_swiglu(*args(gu, 2 * k, None)) == 1
-    assert lib.dg_enqueue_nvfp4_swiglu(*args(gu, 2 * k - 8, _ptr(scratch))) == 1
-    assert lib.dg_enqueue_nvfp4_swiglu(*args(gu.view(-1)[1:], 2 * k, _ptr(scratch))) == 1
+    # blocked scales take the same path; refusals as the GEMV's
+    x = wl.activations(2, k, seed=3).to(dev)
+    out = torch.empty(2, inter, dtype=torch.bfloat16, device=dev)
+    args = lambda xx, i_, kk: (_ptr(xx), xx.stride(0), 1, _ptr(codes), _ptr(scales), 0, _ptr(inverse), _ptr(out), inter,
+                               1, 2, i_, kk, None)
+    assert lib.dg_enqueue_nvfp4_gate_up_swiglu(*args(x, inter, k)) == 0
+    assert lib.dg_enqueue_nvfp4_gate_up_swiglu(*args(x, 0, k)) == 1
+    assert lib.dg_enqueue_nvfp4_gate_up_swiglu(*args(x, inter, k + 16)) == 1
+    torch.cuda.synchronize()

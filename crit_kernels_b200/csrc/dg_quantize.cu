@@ -31,14 +31,21 @@ constexpr unsigned long long kCopyWaitNs = 2000000000ull;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-// The larger of two values, NaN if either is.
-__device__ __forceinline__ float nanmax(float a, float b) { return (a > b || a != a) ? a : b; }
-__device__ __forceinline__ float amax8(const uint4& v, float m) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) m = nanmax(nanmax(m, fabsf(bf16_lo(w[j]))), fabsf(bf16_hi(w[j])));
-  return m;
+// The larger of two values, NaN if either is (one instruction; BF16 pairs keep the maximum exactly).
+__device__ __forceinline__ float nanmax(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
 }
+__device__ __forceinline__ uint32_t amax2(uint32_t pair, uint32_t m) {   // per half: max(|pair|, m), NaN kept
+  uint32_t r;
+  asm("{\n\t.reg .b32 a;\n\tabs.bf16x2 a, %1;\n\tmax.NaN.bf16x2 %0, a, %2;\n\t}" : "=r"(r) : "r"(pair), "r"(m));
+  return r;
+}
+__device__ __forceinline__ uint32_t amax8(const uint4& v, uint32_t m) {
+  return amax2(v.w, amax2(v.z, amax2(v.y, amax2(v.x, m))));
+}
+__device__ __forceinline__ float amax_of(uint32_t m) { return nanmax(bf16_lo(m), bf16_hi(m)); }
 // Two FP32 -> two E4M3 bytes (low byte = lo), round to nearest even, saturating.
 __device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
   uint16_t r;
@@ -50,18 +57,66 @@ __device__ __forceinline__ float e4m3_value(uint32_t byte) {
   asm("{\n\t.reg .b16 t;\n\tcvt.u16.u32 t, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, t;\n\t}" : "=r"(h) : "r"(byte & 0xffu));
   return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu)));
 }
-__device__ __forceinline__ float clamp448(float v) { return v > 448.f ? 448.f : v < -448.f ? -448.f : v; }
-__device__ __forceinline__ uint32_t fp8_pair(uint32_t w, float scale) {   // a BF16 pair over the row scale
-  return e4m3x2(clamp448(__fdiv_rn(bf16_lo(w), scale)), clamp448(__fdiv_rn(bf16_hi(w), scale)));
+// The clamp to +-448 that the quantizer's definition names is the saturating conversion's: every quotient beyond
+// 448 (at most by a rounding of the scale) converts to 448 either way, NaN to NaN.
+//
+// x / d, correctly rounded, for many x over one d whose quotients stay within FP32's normal range (SAFE): with
+// r = RN(1 / d) computed once, q0 = RN(x r), the exact residual e = x - d q0 (one FMA) and q = RN(q0 + e r) give the
+// IEEE quotient: the tail of the usual division sequence without its per-element reciprocal refinement. A zero
+// quotient keeps its own sign where that matters (KEEP_ZERO: the correction would turn -0 into +0). Quotients too
+// small for an exact residual convert to zero whatever their last bits are. Otherwise the full division runs.
+template <bool SAFE, bool KEEP_ZERO>
+__device__ __forceinline__ float quotient(float x, float d, float r) {
+  if constexpr (!SAFE) return __fdiv_rn(x, d);
+  const float q0 = __fmul_rn(x, r);
+  const float q1 = __fmaf_rn(__fmaf_rn(-d, q0, x), r, q0);
+  return KEEP_ZERO && q0 == 0.f ? q0 : q1;
 }
-__device__ __forceinline__ uint32_t fp8_quad(uint32_t w0, uint32_t w1, float scale) {
-  return fp8_pair(w0, scale) | (fp8_pair(w1, scale) << 16);
+template <bool SAFE>
+__device__ __forceinline__ uint32_t fp8_quad(uint32_t w0, uint32_t w1, float d, float r) {
+  return e4m3x2(quotient<SAFE, true>(bf16_lo(w0), d, r), quotient<SAFE, true>(bf16_hi(w0), d, r)) |
+         (e4m3x2(quotient<SAFE, true>(bf16_lo(w1), d, r), quotient<SAFE, true>(bf16_hi(w1), d, r)) << 16);
 }
 
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// The second pass over a row: 16 (or 8) values a thread and store where the output allows it.
+template <bool SAFE>
+__device__ __forceinline__ void quantize_row(const __nv_bfloat16* xr, const uint4* row_smem, uint8_t* qr, int K, float d,
+                                             int staged, bool aligned_in, int vector_out, int tid) {
+  const float r = SAFE ? __frcp_rn(d) : 0.f;
+  if (aligned_in) {
+    const uint4* rv = staged ? row_smem : reinterpret_cast<const uint4*>(xr);
+    if (vector_out && (K & 15) == 0) {   // 16 values -> one 16-byte store
+      for (int i = tid; i < (K >> 4); i += kRowThreads) {
+        const uint4 a = staged ? rv[2 * i] : __ldg(rv + 2 * i), b = staged ? rv[2 * i + 1] : __ldg(rv + 2 * i + 1);
+        reinterpret_cast<uint4*>(qr)[i] = make_uint4(fp8_quad<SAFE>(a.x, a.y, d, r), fp8_quad<SAFE>(a.z, a.w, d, r),
+                                                     fp8_quad<SAFE>(b.x, b.y, d, r), fp8_quad<SAFE>(b.z, b.w, d, r));
+      }
+    } else if (vector_out) {             // 8 values -> one 8-byte store
+      for (int i = tid; i < (K >> 3); i += kRowThreads) {
+        const uint4 a = staged ? rv[i] : __ldg(rv + i);
+        reinterpret_cast<uint2*>(qr)[i] = make_uint2(fp8_quad<SAFE>(a.x, a.y, d, r), fp8_quad<SAFE>(a.z, a.w, d, r));
+      }
+    } else {
+      for (int i = tid; i < (K >> 3); i += kRowThreads) {
+        const uint4 a = staged ? rv[i] : __ldg(rv + i);
+        const uint32_t lo = fp8_quad<SAFE>(a.x, a.y, d, r), hi = fp8_quad<SAFE>(a.z, a.w, d, r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          qr[8 * i + j] = (uint8_t)(lo >> (8 * j));
+          qr[8 * i + 4 + j] = (uint8_t)(hi >> (8 * j));
+        }
+      }
+    }
+  } else {
+    for (int k = tid; k < K; k += kRowThreads)
+      qr[k] = (uint8_t)(e4m3x2(quotient<SAFE, true>(__bfloat162float(xr[k]), d, r), 0.f) & 0xffu);
+  }
 }
 
 // One CTA a row. `staged`: the row (K a multiple of 8, 16-byte aligned, within shared memory) arrives by one bulk copy.
@@ -89,6 +144,7 @@ __global__ void __launch_bounds__(kRowThreads) fp8_rows_kernel(const __nv_bfloat
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");   // x is the previous kernel's output
   float m = 0.f;
+  uint32_t m2 = 0u;   // running maximum of BF16 pairs
   if (staged) {
     if (tid == 0) {
       const uint32_t bytes = (uint32_t)K * 2u;
@@ -114,10 +170,12 @@ __global__ void __launch_bounds__(kRowThreads) fp8_rows_kernel(const __nv_bfloat
     }
     if (!ok) return;
     const uint4* rv = reinterpret_cast<const uint4*>(row_smem);
-    for (int i = tid; i < (K >> 3); i += kRowThreads) m = amax8(rv[i], m);
+    for (int i = tid; i < (K >> 3); i += kRowThreads) m2 = amax8(rv[i], m2);
+    m = amax_of(m2);
   } else if ((K & 7) == 0 && (ldx & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
     const uint4* rv = reinterpret_cast<const uint4*>(xr);
-    for (int i = tid; i < (K >> 3); i += kRowThreads) m = amax8(__ldg(rv + i), m);
+    for (int i = tid; i < (K >> 3); i += kRowThreads) m2 = amax8(__ldg(rv + i), m2);
+    m = amax_of(m2);
   } else {
     for (int k = tid; k < K; k += kRowThreads) m = nanmax(m, fabsf(__bfloat162float(xr[k])));
   }
@@ -135,34 +193,13 @@ __global__ void __launch_bounds__(kRowThreads) fp8_rows_kernel(const __nv_bfloat
   }
   __syncthreads();
   const float sc = row_scale;
-  if (staged || ((K & 7) == 0 && (ldx & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)) {
-    const uint4* rv = staged ? reinterpret_cast<const uint4*>(row_smem) : reinterpret_cast<const uint4*>(xr);
-    if (vector_out && (K & 15) == 0) {   // 16 values -> one 16-byte store
-      for (int i = tid; i < (K >> 4); i += kRowThreads) {
-        const uint4 a = staged ? rv[2 * i] : __ldg(rv + 2 * i), b = staged ? rv[2 * i + 1] : __ldg(rv + 2 * i + 1);
-        reinterpret_cast<uint4*>(qr)[i] =
-            make_uint4(fp8_quad(a.x, a.y, sc), fp8_quad(a.z, a.w, sc), fp8_quad(b.x, b.y, sc), fp8_quad(b.z, b.w, sc));
-      }
-    } else if (vector_out) {             // 8 values -> one 8-byte store
-      for (int i = tid; i < (K >> 3); i += kRowThreads) {
-        const uint4 a = staged ? rv[i] : __ldg(rv + i);
-        reinterpret_cast<uint2*>(qr)[i] = make_uint2(fp8_quad(a.x, a.y, sc), fp8_quad(a.z, a.w, sc));
-      }
-    } else {
-      for (int i = tid; i < (K >> 3); i += kRowThreads) {
-        const uint4 a = staged ? rv[i] : __ldg(rv + i);
-        const uint32_t lo = fp8_quad(a.x, a.y, sc), hi = fp8_quad(a.z, a.w, sc);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          qr[8 * i + j] = (uint8_t)(lo >> (8 * j));
-          qr[8 * i + 4 + j] = (uint8_t)(hi >> (8 * j));
-        }
-      }
-    }
-  } else {
-    for (int k = tid; k < K; k += kRowThreads)
-      qr[k] = (uint8_t)(e4m3x2(clamp448(__fdiv_rn(__bfloat162float(xr[k]), sc)), 0.f) & 0xffu);
-  }
+  const bool aligned_in = staged || ((K & 7) == 0 && (ldx & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0);
+  // a finite scale bounds every quotient of the row by 448 (1 + a rounding): the short division; NaN or infinite
+  // rows take the full one
+  if (sc <= 1e30f)
+    quantize_row<true>(xr, reinterpret_cast<const uint4*>(row_smem), qr, K, sc, staged, aligned_in, vector_out, tid);
+  else
+    quantize_row<false>(xr, reinterpret_cast<const uint4*>(row_smem), qr, K, sc, staged, aligned_in, vector_out, tid);
 }
 
 // Byte offset of block j of row n in cuBLASLt's 128 x 4 tiled scale layout with ct tiles per tile row.
@@ -184,7 +221,7 @@ __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
 // 16 values (8 BF16 pairs) -> scale byte (returned) and 8 code bytes (lo, hi).
 __device__ __forceinline__ uint32_t nvfp4_block(const uint4& v0, const uint4& v1, float g, float g_rcp, uint32_t& lo,
                                                 uint32_t& hi) {
-  const float amax = amax8(v1, amax8(v0, 0.f));
+  const float amax = amax_of(amax8(v1, amax8(v0, 0u)));
   float bs = (amax * kRcp6) * g;
   bs = bs > 448.f ? 448.f : bs;
   const uint32_t sbits = e4m3x2(bs, 0.f) & 0xffu;
@@ -193,11 +230,24 @@ __device__ __forceinline__ uint32_t nvfp4_block(const uint4& v0, const uint4& v1
   d = d < 1e-30f ? 1e-30f : d;
   const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
   lo = hi = 0u;
+  if (zero) return sbits;
+  // a block whose quotients cannot leave FP32's range takes the short division (a zero quotient's sign is dropped by
+  // the conversion's + 0 anyway); the rest (values near FP32's limits) the full one
+  if (amax < 1e8f) {
+    const float r = __frcp_rn(d);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t byte = zero ? 0u : e2m1x2(__fdiv_rn(bf16_lo(w[i]), d), __fdiv_rn(bf16_hi(w[i]), d));
-    if (i < 4) lo |= byte << (8 * i);
-    else hi |= byte << (8 * (i - 4));
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t byte = e2m1x2(quotient<true, false>(bf16_lo(w[i]), d, r), quotient<true, false>(bf16_hi(w[i]), d, r));
+      if (i < 4) lo |= byte << (8 * i);
+      else hi |= byte << (8 * (i - 4));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t byte = e2m1x2(__fdiv_rn(bf16_lo(w[i]), d), __fdiv_rn(bf16_hi(w[i]), d));
+      if (i < 4) lo |= byte << (8 * i);
+      else hi |= byte << (8 * (i - 4));
+    }
   }
   return sbits;
 }

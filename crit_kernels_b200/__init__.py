@@ -2,9 +2,9 @@
 
 `get_kernel("crit-labs/decode-gemv", version=1)` returns the `decode_gemv` module with the reference's surface
 (`gemv`, `gemv_fp8`, `gemv_bf16`, `hardware_decode`, `CUDA_ROWS`), as `kernels.get_kernel` does for the reference
-(crit-kernels README.md:32-36, decode-gemv/tests/test_decode_gemv.py:14). The package directory is also laid out so
-that `LOCAL_KERNELS=crit-labs/decode-gemv=<this directory>` works with the real `kernels` loader where it is
-installed.
+(crit-kernels README.md:32-36, decode-gemv/tests/test_decode_gemv.py:14). This function is the loader: the
+`build/<variant>/` tree with `metadata.json` that the real `kernels` package loads is kernel-builder's output and is
+not produced by this package's builder.
 """
 from __future__ import annotations
 

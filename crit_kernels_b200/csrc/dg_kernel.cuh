@@ -14,9 +14,10 @@
 //     Bytes in flight are set by the ring (up to ~200 KB per SM), not by registers. Where the arithmetic, not HBM,
 //     is the limit (larger M) the CTA has no producer warp: its consumer warps issue the same copies between stages.
 //   * consumer warp w owns rows w, w+C, ... of the tile. Lane l owns the 16-byte blocks l, l+32, ... of each row and
-//     keeps two FP32 chains per (row, m): even and odd elements, advanced together by one packed fma.rn.f32x2. The
-//     chains visit the blocks in ascending order, the two chains are added, and one xor-shuffle tree (16, 8, 4, 2, 1)
-//     adds the lanes; the row scale multiplies once and the result is rounded once to the output type.
+//     keeps two FP32 chains per (row, m): even and odd elements, advanced together by one packed fma.rn.f32x2 or, where
+//     the arithmetic is the limit, by two mixed-precision fma.rn.f32.bf16 / .f16 (same bits: the products are exact).
+//     The chains visit the blocks in ascending order, the two chains are added, and one xor-shuffle tree (16, 8, 4, 2,
+//     1) adds the lanes; the row scale multiplies once and the result is rounded once to the output type.
 //
 // A row's summation order is therefore a function of K and the format alone: it does not depend on M, on the rows a
 // warp holds, on the tile or window sizes the launch picked, on the CTA count, or on which slice of the matrix a
@@ -72,7 +73,8 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 //             hosts the same number of consumers.
 //   class 1   M medium: 11 consumer + 1 producer warps, or 12 consumer warps that issue the copies themselves
 //             (168 registers each).
-//   class 2   M large: the kernel is FP32-FMA-bound. 8 consumer warps, 255 registers each, no producer warp.
+//   class 2   M large: the kernel is FP32-FMA-bound. No producer warp; 8 to 16 consumer warps by (format, M), see
+//             class2_warps / class2_rows.
 //             In classes 1 and 2 the consumers' instruction issue is the limit and a sub-partition's time is that of
 //             the consumers it hosts, so the consumers should be spread evenly: one producer warp keeps up with the
 //             copies and leaves one sub-partition a consumer short (measured against 10 + 2 and 6 + 2 warps: 4-8 %

@@ -101,9 +101,12 @@ DeviceState* device_state() {
   bool ok = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) == cudaSuccess && major == 10 &&
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0 &&
             cudaGetSymbolAddress(&status, dg_status_word) == cudaSuccess;
+  // (the carveout preference keeps the SM's whole shared memory available where two CTAs are to share it)
   for (const void* const* table : kTables)
     for (int m = 0; ok && m < 16; ++m)
-      ok = cudaFuncSetAttribute(table[m], cudaFuncAttributeMaxDynamicSharedMemorySize, dg::kSmemLimit) == cudaSuccess;
+      ok = cudaFuncSetAttribute(table[m], cudaFuncAttributeMaxDynamicSharedMemorySize, dg::kSmemLimit) == cudaSuccess &&
+           cudaFuncSetAttribute(table[m], cudaFuncAttributePreferredSharedMemoryCarveout,
+                                cudaSharedmemCarveoutMaxShared) == cudaSuccess;
   for (int m = 0; ok && m < 16; ++m)
     ok = cudaFuncSetAttribute(dg_batch_table_nvfp4_bf16[m], cudaFuncAttributeMaxDynamicSharedMemorySize,
                               dg::kSmemLimit) == cudaSuccess;
@@ -132,12 +135,21 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 //                   DRAM efficiency and per-row bulk copies are issue-limited), up to four when a tile has few rows;
 //                   activations under 32 KB per stage
 //   stages          as many as fit in shared memory, at most kMaxStages
+// Dynamic shared memory a CTA may take: all of an SM's, or its share where several CTAs live on one SM together
+// (the system keeps 1 KB per CTA).
+int smem_limit(int fmt, int M) {
+  const int share = dg::ctas_per_sm(fmt, M);
+  return share == 1 ? dg::kSmemLimit : ((dg::kSmemLimit + 1024) / share - 1024) & ~127;
+}
+
 bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem, int grid = 0) {
   const FormatInfo f = kFormats[fmt];
   const int cw = dg::consumer_warps(fmt, M);
   const long long row_bits = (long long)K * 128 / f.e;   // 16 bytes per e elements
   p.row_bytes = (int)(row_bits / 8);
   p.nblk = p.row_bytes / 16;
+  const int share = dg::ctas_per_sm(fmt, M);   // CTAs that live on one SM together
+  sms *= share;
   ctas = grid > 0 ? grid : sms < ceil_div(N, 4) ? sms : ceil_div(N, 4);   // grid: the launch is shared (batch)
   const int rows_per_cta = ceil_div(N, ctas);
   const int per_warp = ceil_div(rows_per_cta, cw);
@@ -167,7 +179,7 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   p.stage_bytes = (steps * (rows_cap * dg::kStepBytes + x_step) +
                    p.rows_per_warp * dg::scale_group_bytes(cw, steps, f.scb) + 127) & ~127;
   const int behind = p.pairs ? dg::kMeetBytes : 0;   // the SwiGLU epilogue's meeting place lies behind the ring
-  int stages = (dg::kSmemLimit - dg::kSmemHeader - behind) / p.stage_bytes;
+  int stages = (smem_limit(fmt, M) - dg::kSmemHeader - behind) / p.stage_bytes;
   if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return false;
   p.stages = stages;
@@ -420,20 +432,20 @@ int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf1
     }
     int ctas = 0, smem = 0;
     // one grid for all: a CTA per SM, whatever a GEMV's size (a CTA without rows of a GEMV passes it by)
-    if (const int code = prepare(dg::FMT_NVFP4, p, M, ctas, smem, st->sms)) return code;
+    if (const int code = prepare(dg::FMT_NVFP4, p, M, ctas, smem, st->sms * dg::ctas_per_sm(dg::FMT_NVFP4, M))) return code;
     if (p.stage_bytes > stage_bytes) stage_bytes = p.stage_bytes;
     out[g] = p;
   }
   // one ring for all: the largest stage any GEMV needs, as many of them as fit
   // (behind the ring: room for one GEMV's parameters, which kernels without producer warps keep there)
-  int stages = (dg::kSmemLimit - dg::kSmemHeader - (int)sizeof(Params)) / stage_bytes;
+  int stages = (smem_limit(dg::FMT_NVFP4, M) - dg::kSmemHeader - (int)sizeof(Params)) / stage_bytes;
   if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return (int)cudaErrorInvalidValue;
   for (int g = 0; g < count; ++g) {
     out[g].stage_bytes = stage_bytes;
     out[g].stages = stages;
   }
-  head.magic = kBatchMagic; head.count = count; head.M = M; head.ctas = st->sms;
+  head.magic = kBatchMagic; head.count = count; head.M = M; head.ctas = st->sms * dg::ctas_per_sm(dg::FMT_NVFP4, M);
   head.smem = dg::kSmemHeader + stages * stage_bytes + (int)sizeof(Params);
   head.threads = 32 * (dg::consumer_warps(dg::FMT_NVFP4, M) + dg::producer_warps(dg::FMT_NVFP4, M));
   head.device_blob = device_blob;

@@ -68,7 +68,8 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 
 // CTA shape per (format, M): a speed choice, never a row's bits. Register need decides it: the accumulators take
 // 2 * rows * M registers and the held operand (activations or decoded weights) 8-16 per activation row or weight row.
-//   class 0   M small: the kernel is HBM-bound. 12 consumer + 4 producer warps (128 registers each): as many warps
+//   class 0   M small: the kernel is HBM-bound. 12 consumer + 4 producer warps (14 + 2 where two_producers says so;
+//             128 registers each): as many warps
 //             as the register file gives, to hide shared-memory and conversion latencies; every SM sub-partition
 //             hosts the same number of consumers.
 //   class 1   M medium: 11 consumer + 1 producer warps, or 12 consumer warps that issue the copies themselves
@@ -89,14 +90,23 @@ template <> struct Format<FMT_NVFP4> { static constexpr int E = 32, SCB = 64; };
 __host__ __device__ constexpr int shape_class(int fmt, int m) {
   return fmt == FMT_NVFP4 ? (m <= 2 ? 0 : m <= 4 ? 1 : 2) : (m <= 4 ? 0 : m <= 8 ? 1 : 2);
 }
+// CTAs that share an SM (each with its share of the shared memory; the grid is this many per SM). BF16 class 0 runs
+// two CTAs of 7 + 1 warps: the next kernel's CTA moves in and starts its copies as soon as the first of the two
+// leaves (3-7 % faster over back-to-back calls at 8192 x 8192 than one CTA of 14 + 2; the other formats measured
+// 10-20 % slower as two CTAs of 6 + 2 than as one of 12 + 4).
+__host__ __device__ constexpr int ctas_per_sm(int fmt, int m) { return fmt == FMT_BF16 && shape_class(fmt, m) == 0 ? 2 : 1; }
 __host__ __device__ constexpr bool few_rows(int fmt, int m) { return shape_class(fmt, m) < 2; }
-// (BF16 weights, the lightest arithmetic per byte, measured 13-19 % faster with 14 + 2 warps than with 12 + 4.)
+// (BF16 weights, the lightest arithmetic per byte, measured 13-19 % faster with 14 + 2 warps per SM than with 12 + 4;
+// they run as two CTAs of 7 + 1, see ctas_per_sm.)
 // class 1 of the formats with the lighter arithmetic per byte (BF16, MXFP8) and class 2 of all: no producer warp.
 __host__ __device__ constexpr bool self_fed(int fmt, int m) {
   return shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && (fmt == FMT_BF16 || fmt == FMT_MXFP8));
 }
 // Class 2 by (format, M), measured on 28672 x 8192 (16384 x 8192 for BF16) over the candidates 8 warps x 4 rows,
 // 12 x 3, 12 x 4 and 16 x 2 (255, 168, 168 and 128 registers per thread): up to 14 % between them.
+// Class 0 with 14 + 2 warps instead of 12 + 4: FP8 and NVFP4 at M <= 2 measured 1.5-2 % faster at 28672 x 8192 and
+// NVFP4 7 % faster at 8192 x 8192 (M = 1); MXFP8 measured 10 % slower at M = 2 and stays.
+__host__ __device__ constexpr bool two_producers(int fmt, int m) { return (fmt == FMT_FP8 || fmt == FMT_NVFP4) && m <= 2; }
 __host__ __device__ constexpr int class2_warps(int fmt, int m) {
   return fmt == FMT_FP8 ? (m <= 13 ? 12 : 8)
          : fmt == FMT_BF16 ? (m <= 11 ? 12 : 8)
@@ -106,11 +116,11 @@ __host__ __device__ constexpr int class2_rows(int fmt, int m) {
   return fmt == FMT_NVFP4 ? (m == 5 || m == 8 ? 4 : m <= 11 ? 3 : 2) : 4;
 }
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 14 : 12)
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 7 : two_producers(fmt, m) ? 14 : 12)
          : shape_class(fmt, m) == 1 ? (self_fed(fmt, m) ? 12 : 11) : class2_warps(fmt, m);
 }
 __host__ __device__ constexpr int producer_warps(int fmt, int m) {
-  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 2 : 4) : self_fed(fmt, m) ? 0 : 1;
+  return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 1 : two_producers(fmt, m) ? 2 : 4) : self_fed(fmt, m) ? 0 : 1;
 }
 // Kernels that advance their chains with the mixed-precision FMA instead of the packed FP32 FMA (same bits; see f2):
 // where the arithmetic is the limit, one issue slot per product without any conversion of the activations beats
@@ -1388,7 +1398,7 @@ __device__ __forceinline__ void ring_setup(const Params& p, uint32_t full0, uint
 }
 
 template <int FMT, int M, typename XT>
-__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, 1)
+__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, ctas_per_sm(FMT, M))
     gemv_kernel(const __grid_constant__ Params p) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);
@@ -1429,7 +1439,7 @@ __global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, 
 // finished them and goes on; the arrivals of all GEMVs are exchanged once, at the end. For GEMVs whose inputs do not
 // depend on each other's outputs only (all activations are read after one wait for the previous kernel).
 template <int FMT, int M, typename XT>
-__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, 1)
+__global__ void __launch_bounds__((consumer_warps(FMT, M) + producer_warps(FMT, M)) * 32, ctas_per_sm(FMT, M))
     gemv_batch_kernel(const Params* __restrict__ items, int count) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int CW = consumer_warps(FMT, M), PW = producer_warps(FMT, M);

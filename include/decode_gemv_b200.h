@@ -236,7 +236,7 @@ DG_API int dg_set_static_weights(int enabled);
  * consumer warp finished its rows, 4 its last warp left; s = 5 is the SM id. Launches beyond `launches` are not
  * traced; buffer = NULL switches tracing off (the default: the kernels then only test one pointer). Process-wide,
  * host only. No counterpart in the reference. */
-#define DG_TRACE_CTAS 160
+#define DG_TRACE_CTAS 320
 #define DG_TRACE_SLOTS 8
 DG_API int dg_set_trace(void* buffer, int launches);
 

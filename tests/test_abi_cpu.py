@@ -33,8 +33,9 @@ def test_plans_fit_the_device_and_do_not_depend_on_the_call(fmt, n, k):
     for m in range(1, 17):
         p = cabi.plan(fmt, m, n, k)
         assert p == cabi.plan(fmt, m, n, k)
-        assert 1 <= p["ctas"] <= 148 and p["ctas"] <= n
-        assert p["stages"] >= 2 and p["smem_bytes"] <= 232448
+        # one CTA per SM with all its shared memory, or two that share it (1 KB per CTA is the system's)
+        assert 1 <= p["ctas"] <= 296 and p["ctas"] <= n
+        assert p["stages"] >= 2 and p["smem_bytes"] <= (232448 if p["ctas"] <= 148 else 115712)
         assert p["smem_bytes"] == 256 + p["stages"] * p["stage_bytes"]
         assert 1 <= p["rows_per_warp"] <= 8 and 1 <= p["steps"] <= 8
 

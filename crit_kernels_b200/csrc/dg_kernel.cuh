@@ -103,17 +103,25 @@ __host__ __device__ constexpr bool self_fed(int fmt, int m) {
   return shape_class(fmt, m) == 2 || (shape_class(fmt, m) == 1 && (fmt == FMT_BF16 || fmt == FMT_MXFP8));
 }
 // Class 2 by (format, M), measured on 28672 x 8192 (16384 x 8192 for BF16) over the candidates 8 warps x 4 rows,
-// 12 x 3, 12 x 4 and 16 x 2 (255, 168, 168 and 128 registers per thread): up to 14 % between them.
+// 12 x 3, 12 x 4 and 16 x 2 (255, 168, 168 and 128 registers per thread): up to 14 % between them. NVFP4 also on
+// 8192 x 8192, 8192 x 28672 and 57344 x 8192: at M = 8 the 16 x 2 shape is 2 % ahead of 8 x 4 on the large matrices
+// and 20-23 % on the two with 8192 rows (55 rows per CTA).
 // Class 0 with 14 + 2 warps instead of 12 + 4: FP8 and NVFP4 at M <= 2 measured 1.5-2 % faster at 28672 x 8192 and
 // NVFP4 7 % faster at 8192 x 8192 (M = 1); MXFP8 measured 10 % slower at M = 2 and stays.
 __host__ __device__ constexpr bool two_producers(int fmt, int m) { return (fmt == FMT_FP8 || fmt == FMT_NVFP4) && m <= 2; }
 __host__ __device__ constexpr int class2_warps(int fmt, int m) {
+#ifdef DG_C2W
+  if (fmt == DG_C2FMT && m >= DG_C2LO && m <= DG_C2HI) return DG_C2W;
+#endif
   return fmt == FMT_FP8 ? (m <= 13 ? 12 : 8)
-         : fmt == FMT_BF16 ? (m <= 11 ? 12 : 8)
-         : fmt == FMT_NVFP4 ? (m == 8 ? 8 : m <= 11 ? 12 : 16) : 8;
+         : fmt == FMT_BF16 ? (m <= 14 ? 12 : 8)
+         : fmt == FMT_NVFP4 ? (m == 8 || m >= 11 ? 16 : 12) : 8;
 }
 __host__ __device__ constexpr int class2_rows(int fmt, int m) {
-  return fmt == FMT_NVFP4 ? (m == 5 || m == 8 ? 4 : m <= 11 ? 3 : 2) : 4;
+#ifdef DG_C2W
+  if (fmt == DG_C2FMT && m >= DG_C2LO && m <= DG_C2HI) return DG_C2R;
+#endif
+  return fmt == FMT_NVFP4 ? (m == 5 ? 4 : m == 8 || m >= 11 ? 2 : 3) : fmt == FMT_BF16 && m >= 12 && m <= 14 ? 3 : 4;
 }
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
   return shape_class(fmt, m) == 0 ? (fmt == FMT_BF16 ? 7 : two_producers(fmt, m) ? 14 : 12)

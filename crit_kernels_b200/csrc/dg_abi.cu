@@ -163,8 +163,12 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   if (p.pairs) p.rows_per_warp = p.rows_per_warp >= 4 ? 4 : 2;   // gate and up rows side by side: an even count
   const int rows_cap = cw * p.rows_per_warp;
   const int w_step = rows_cap * (dg::kStepBytes + f.scb);   // sizing estimate; the exact stage size is below
-  const int x_step = M * 64 * f.e;
   const int row_steps = ceil_div(p.nblk, 32);
+  // Activations that are small enough stay in shared memory for the whole kernel (behind the ring) instead of passing
+  // through the stages: one launch's only (a batch's GEMVs each have their own).
+  const int resident_bytes = row_steps * M * 64 * f.e + ((row_steps + 15) & ~15);
+  p.x_resident = grid == 0 && dg::resident_capable(fmt, M) && resident_bytes <= dg::kResidentLimit;
+  const int x_step = p.x_resident ? 0 : M * 64 * f.e;
   int steps = ceil_div(32768, w_step);
   if (steps < 2) steps = 2;
   if (steps > 4) steps = 4;   // a tensor-copy box is at most 256 eight-byte elements (2 KB) wide
@@ -178,11 +182,13 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   p.steps = steps;
   p.stage_bytes = (steps * (rows_cap * dg::kStepBytes + x_step) +
                    p.rows_per_warp * dg::scale_group_bytes(cw, steps, f.scb) + 127) & ~127;
-  const int behind = p.pairs ? dg::kMeetBytes : 0;   // the SwiGLU epilogue's meeting place lies behind the ring
+  // behind the ring: the SwiGLU epilogue's meeting place, then the resident activations
+  const int behind = (p.pairs ? dg::kMeetBytes : 0) + (p.x_resident ? resident_bytes : 0);
   int stages = (smem_limit(fmt, M) - dg::kSmemHeader - behind) / p.stage_bytes;
   if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return false;
   p.stages = stages;
+  p.x_res_off = dg::kSmemHeader + stages * p.stage_bytes + (p.pairs ? dg::kMeetBytes : 0);
   smem = dg::kSmemHeader + stages * p.stage_bytes + behind;
   return true;
 }

@@ -32,6 +32,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <type_traits>
 
 #include "dg_swiglu.cuh"
 
@@ -143,6 +144,28 @@ __host__ __device__ constexpr bool use_mixed(int fmt, int m) {
 __host__ __device__ constexpr int rows_max(int fmt, int m) {
   return shape_class(fmt, m) == 2 ? class2_rows(fmt, m) : 4;
 }
+// Resident activations (Params::x_resident, decided by the launch plan): class 0 of FP8 / NVFP4, where the whole
+// [M][K] activations are small, keeps them in shared memory behind the ring for the whole kernel instead of copying a
+// window of them into every ring stage: the consumer warps fetch them once, while the first weights are on their way.
+__host__ __device__ constexpr bool resident_capable(int fmt, int m) {
+  return (fmt == FMT_FP8 || fmt == FMT_NVFP4) && shape_class(fmt, m) == 0;
+}
+constexpr int kResidentLimit = 40 * 1024;   // bytes of activations (and their flags) a kernel keeps resident at most
+// How a kernel instance advances its chains, by the activations' type too.
+//   MIXED     the mixed-precision FMA throughout: use_mixed, and every FP16-activation kernel of the formats whose
+//             decoded weights are FP16 values already (E4M3, E2M1): nothing is converted at all.
+//   HALF_RES  BF16 activations of a resident_capable kernel: when the activations are resident, each 512-byte step
+//             of them (64 * E elements of every activation row) is kept as FP16 if every value of it is an FP16
+//             value too (zero, or 2^-14 <= |x| <= 65504: FP16 carries BF16's 8 significant bits), and the consumers
+//             run the FP16 mixed-FMA body on that step: about 2 instead of 3.5 instructions per weight at M = 1. A
+//             step with any other value (tiny, huge, infinite, NaN) stays BF16 and takes the packed FP32 body. Every
+//             product is exact either way and the additions are the same, so are the bits.
+template <int FMT, int M, typename XT>
+struct Arithmetic {
+  static constexpr bool HALF_X = std::is_same<XT, __half>::value;
+  static constexpr bool MIXED = use_mixed(FMT, M) || (HALF_X && (FMT == FMT_FP8 || FMT == FMT_NVFP4));
+  static constexpr bool HALF_RES = !HALF_X && !MIXED && resident_capable(FMT, M);
+};
 
 struct Params {
   const void* x;             // [M][ldx] BF16 or FP16
@@ -169,6 +192,10 @@ struct Params {
   // [pairs, 2 pairs); N counts the rows as the tiles walk them (see Walk). A warp holds row k of both halves side by
   // side and writes out[m][k] = silu(gate) * up (FP32, one rounding) instead of the two sums: `pairs` columns.
   int pairs;
+  // Resident activations (resident_capable kernels; 0 = the activations travel through the ring stages): the
+  // kernel's dynamic shared memory holds, x_res_off bytes in, ceil(nblk / 32) steps of [M][64 * E elements] laid out
+  // as in a stage, then one flag byte per step (1 = the step is held as FP16, see Arithmetic::HALF_RES).
+  int x_resident, x_res_off;
   unsigned long long* trace; // diagnostic (dg_set_trace): kTraceSlots time stamps per CTA, or null
   unsigned long long wait_limit_ns;   // every wait in the kernel gives up after this long (status word, then leaves)
   // All-gather epilogue (world >= 1, 0 = off): this rank's [M][N] results go into slot `rank` of its own
@@ -205,6 +232,17 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
 __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts_u8(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ldg_nc128(const void* ptr) {   // memory nobody writes while the kernel runs
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
   return v;
 }
 
@@ -595,6 +633,12 @@ struct Producer {
   // Activations of iteration `it`: wbytes / 16 blocks of E elements per row, 16 bytes (8 elements) per copy; then
   // this lane's arrival, which fires when its copies have landed.
   __device__ __forceinline__ void activations(int it, int s) const {
+    if constexpr (resident_capable(FMT, M)) {
+      if (p.x_resident) {   // nothing to copy: the lane's arrival alone
+        cp_async_arrive_noinc(full0 + 8u * s);
+        return;
+      }
+    }
     const int win = it % wk.nwin;
     const uint32_t full = full0 + 8u * s;
     const uint32_t stage = ring + (uint32_t)s * p.stage_bytes;
@@ -1047,6 +1091,86 @@ __device__ __forceinline__ int lane_value(int lane, int slot) {
 // ---------------------------------------------------------------------------------------------------------------
 // One tile for one consumer warp holding up to R rows (nr of them real).
 
+// Eight BF16 values as eight FP16 values, and whether that is exact for all of them with normal results (zero, or
+// 2^-14 <= |x| <= 65504; NaN and the infinities say no): the test of Arithmetic::HALF_RES.
+__device__ __forceinline__ bool bf16x2_fits_half(uint32_t v, uint32_t& h) {
+  const float lo = __uint_as_float(v << 16), hi = __uint_as_float(v & 0xffff0000u);
+  const __half2 t = __floats2half2_rn(lo, hi);
+  h = *reinterpret_cast<const uint32_t*>(&t);
+  const float alo = fabsf(lo), ahi = fabsf(hi);
+  return (alo == 0.f || (alo >= 6.103515625e-05f && alo <= 65504.f)) &&
+         (ahi == 0.f || (ahi >= 6.103515625e-05f && ahi <= 65504.f));
+}
+__device__ __forceinline__ bool bf16x8_fits_half(const uint4& v, uint4& h) {
+  const bool a = bf16x2_fits_half(v.x, h.x), b = bf16x2_fits_half(v.y, h.y);
+  const bool c = bf16x2_fits_half(v.z, h.z), d = bf16x2_fits_half(v.w, h.w);
+  return a && b && c && d;
+}
+
+// Resident activations: the consumer warps bring the whole [M][K] activations into shared memory, once per kernel.
+// Warp w takes steps w, w + CW, ...; of a step, lane l holds slots l, l + 32, ... (16 bytes each) of every activation
+// row and stores them where a ring stage would have them. BF16 activations (HALF) are tested on the way: the warp
+// stores a step as FP16 if all of its values allow it, as loaded otherwise, and says which in the step's flag byte.
+// Ends with a barrier of the consumer warps.
+template <int FMT, int M, int CW, bool HALF>
+__device__ __forceinline__ void fill_resident(const Params& p, unsigned char* smem) {
+  constexpr int E = Format<FMT>::E, NQ = E / 8;
+  const int nsteps = (p.nblk + 31) >> 5, slots = p.nblk * NQ;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t base = smem_addr(smem) + (uint32_t)p.x_res_off;
+  const uint32_t flags = base + (uint32_t)nsteps * (M * 64 * E);
+  const unsigned char* xg = reinterpret_cast<const unsigned char*>(p.x);
+  for (int st = warp; st < nsteps; st += CW) {
+    uint4 v[M][NQ];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) {
+        const int sl = st * (32 * NQ) + j * 32 + lane;
+        v[m][j] = sl < slots ? ldg_nc128(xg + (size_t)m * p.ldx * 2 + (size_t)sl * 16) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    bool fits = false;
+    if constexpr (HALF) {
+      uint4 h[M][NQ];
+      fits = true;
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int j = 0; j < NQ; ++j) fits &= bf16x8_fits_half(v[m][j], h[m][j]);   // (slots past the end hold zeros)
+      fits = __all_sync(0xffffffffu, fits);
+      if (fits) {
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int j = 0; j < NQ; ++j) v[m][j] = h[m][j];
+      }
+    }
+    const uint32_t dst = base + (uint32_t)st * (M * 64 * E);
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+      for (int j = 0; j < NQ; ++j) sts128(dst + m * (64 * E) + swizzle_slot<NQ>(j * 32 + lane) * 16, v[m][j]);
+    if (lane == 0) sts_u8(flags + st, fits ? 1u : 0u);
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+}
+
+// The two chains between their two forms (a step that could not be kept as FP16 takes the packed body).
+template <int R, int M>
+__device__ __forceinline__ void to_packed(const f2 (&a)[R][M], pk2 (&b)[R][M]) {
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) b[r][m] = pack2(a[r][m].lo, a[r][m].hi);
+}
+template <int R, int M>
+__device__ __forceinline__ void from_packed(const pk2 (&b)[R][M], f2 (&a)[R][M]) {
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) asm("mov.b64 {%0, %1}, %2;" : "=f"(a[r][m].lo), "=f"(a[r][m].hi) : "l"(b[r][m].v));
+}
+
 template <bool MIXED> struct Chains;   // accumulator pair type of a kernel
 template <> struct Chains<false> {
   using type = pk2;
@@ -1073,7 +1197,8 @@ __device__ __forceinline__ void self_fill(const Params& p, const Params& maps, c
     Producer<FMT, M, CW, CW>(p, maps, wk, lay, smem, full0, empty0, (int)threadIdx.x).activations_shared(it, s);
 }
 
-template <int FMT, int M, int R, typename XT, int CW, bool SELF>
+// RES: the activations are resident (Params::x_resident), not in the stages.
+template <int FMT, int M, int R, typename XT, int CW, bool SELF, bool RES = false>
 __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps, const Walk<CW>& wk,
                                              const StageLayout<FMT, M, CW>& lay,
                                              unsigned char* smem, uint32_t full0, uint32_t empty0,
@@ -1081,15 +1206,16 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
                                              int& it) {
   constexpr int E = Format<FMT>::E, SCB = Format<FMT>::SCB, NQ = E / 8;
   constexpr bool FEW = few_rows(FMT, M);
-  constexpr bool MIXED = use_mixed(FMT, M);
-  using Acc = typename Chains<MIXED>::type;
+  constexpr bool MIXED = Arithmetic<FMT, M, XT>::MIXED;
+  constexpr bool HALF = RES && Arithmetic<FMT, M, XT>::HALF_RES;   // steps flagged as FP16 take the mixed body
+  using Acc = typename Chains<MIXED || HALF>::type;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const XOffsets<NQ> xo(lane);
   Acc acc[R][M];
 #pragma unroll
   for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = Chains<MIXED>::zero();
+    for (int m = 0; m < M; ++m) acc[r][m] = Chains<MIXED || HALF>::zero();
   // Offsets of the warp's rows inside a stage (rows are CW tile rows and one scale group apart); rows the warp does
   // not have alias its last real row (their sums are discarded).
   uint32_t woff[R], scoff[R];
@@ -1128,13 +1254,29 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
         const int blk = blk0 + st * 32 + lane;
         if (blk < p.nblk) {
           const uint32_t wrow = stage + st * kStepBytes;
-          const uint32_t xs = stage + lay.x_off + st * (M * 64 * E);
+          const int res_step = win * p.steps + st;   // the step's place among the resident ones
+          const uint32_t xs = RES ? smem_addr(smem) + (uint32_t)p.x_res_off + (uint32_t)res_step * (M * 64 * E)
+                                  : stage + lay.x_off + st * (M * 64 * E);
+          bool as_half = false;
+          if constexpr (HALF)
+            as_half = lds_u8(smem_addr(smem) + (uint32_t)p.x_res_off + (uint32_t)((p.nblk + 31) >> 5) * (M * 64 * E) +
+                             res_step) != 0;
           if constexpr (FMT == FMT_BF16) {
             if constexpr (MIXED) body_bf16_mixed<M, R>(wrow, woff, xs + lane * 16, acc);
             else body_bf16<FEW, M, R, XT>(wrow, woff, xs + lane * 16, acc);
           } else if constexpr (FMT == FMT_FP8) {
             if constexpr (MIXED) {
               body_fp8_mixed<M, R, XT>(wrow, woff, xs, xo, acc);
+            } else if constexpr (HALF) {
+              if (as_half) {
+                body_fp8_mixed<M, R, __half>(wrow, woff, xs, xo, acc);
+              } else {
+                float none[R];
+                pk2 packed[R][M];
+                to_packed<R, M>(acc, packed);
+                body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, xo, packed);
+                from_packed<R, M>(packed, acc);
+              }
             } else {
               float none[R];
               body_fp8<FEW, false, M, R, XT>(wrow, woff, none, xs, xo, acc);
@@ -1166,8 +1308,20 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
                 sc[r] = e4m3x2_to_f32(__ldg(reinterpret_cast<const uint16_t*>(p.scales + off)));
               }
             }
-            if constexpr (MIXED) body_nvfp4_mixed<M, R, XT>(wrow, woff, sc, xs, xo, acc);
-            else body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, xo, acc);
+            if constexpr (MIXED) {
+              body_nvfp4_mixed<M, R, XT>(wrow, woff, sc, xs, xo, acc);
+            } else if constexpr (HALF) {
+              if (as_half) {
+                body_nvfp4_mixed<M, R, __half>(wrow, woff, sc, xs, xo, acc);
+              } else {
+                pk2 packed[R][M];
+                to_packed<R, M>(acc, packed);
+                body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, xo, packed);
+                from_packed<R, M>(packed, acc);
+              }
+            } else {
+              body_nvfp4<FEW, M, R, XT>(wrow, woff, sc, xs, xo, acc);
+            }
           }
         }
       }
@@ -1355,6 +1509,11 @@ __device__ __forceinline__ bool consume_gemv(const Params& p, const Params& maps
   } else if (first) {
     griddep_wait();   // consumers read scales and write results in global memory: after the previous kernel
   }
+  bool resident = false;
+  if constexpr (resident_capable(FMT, M) && !SELF) {
+    resident = p.x_resident != 0;
+    if (resident) fill_resident<FMT, M, CW, Arithmetic<FMT, M, XT>::HALF_RES>(p, smem);
+  }
   if (first && threadIdx.x == 0) trace_stamp(p.trace, TRACE_DEP);
   int it = 0;
   bool ok = true;
@@ -1367,16 +1526,22 @@ __device__ __forceinline__ bool consume_gemv(const Params& p, const Params& maps
     }
     // three rows have their own code only where tiles of odd heights are made on purpose (split tails)
     constexpr bool THREE = M == 1 && RMAX == 4;
-    if (nr > (THREE ? 3 : 2))
-      ok = consume_tile<FMT, M, RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity,
-                                                    it);
-    else if (THREE && nr > 2)
-      ok = consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr,
-                                                               s, parity, it);
-    else if (nr > 1)
-      ok = consume_tile<FMT, M, 2, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity, it);
-    else
-      ok = consume_tile<FMT, M, 1, XT, CW, SELF>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity, it);
+    auto tile = [&](auto res) {
+      constexpr bool RES = decltype(res)::value;
+      if (nr > (THREE ? 3 : 2))
+        return consume_tile<FMT, M, RMAX, XT, CW, SELF, RES>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s,
+                                                             parity, it);
+      if (THREE && nr > 2)
+        return consume_tile<FMT, M, THREE ? 3 : RMAX, XT, CW, SELF, RES>(p, maps, wk, lay, smem, full0, empty0, abort_flag,
+                                                                        t, nr, s, parity, it);
+      if (nr > 1)
+        return consume_tile<FMT, M, 2, XT, CW, SELF, RES>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s,
+                                                          parity, it);
+      return consume_tile<FMT, M, 1, XT, CW, SELF, RES>(p, maps, wk, lay, smem, full0, empty0, abort_flag, t, nr, s, parity,
+                                                        it);
+    };
+    if constexpr (resident_capable(FMT, M) && !SELF) ok = resident ? tile(std::true_type()) : tile(std::false_type());
+    else ok = tile(std::false_type());
   }
   if (!ok && (threadIdx.x & 31) == 0 && p.status) atomicOr(p.status, kStatusConsumerTimeout);
   return ok;

@@ -164,32 +164,46 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   const int rows_cap = cw * p.rows_per_warp;
   const int w_step = rows_cap * (dg::kStepBytes + f.scb);   // sizing estimate; the exact stage size is below
   const int row_steps = ceil_div(p.nblk, 32);
-  // Activations that are small enough stay in shared memory for the whole kernel (behind the ring) instead of passing
-  // through the stages: one launch's only (a batch's GEMVs each have their own).
-  const int resident_bytes = row_steps * M * 64 * f.e + ((row_steps + 15) & ~15);
-  p.x_resident = grid == 0 && dg::resident_capable(fmt, M) && resident_bytes <= dg::kResidentLimit;
-  const int x_step = p.x_resident ? 0 : M * 64 * f.e;
-  int steps = ceil_div(32768, w_step);
-  if (steps < 2) steps = 2;
-  if (steps > 4) steps = 4;   // a tensor-copy box is at most 256 eight-byte elements (2 KB) wide
-  // BF16 rows are the longest per K: 1.5 KB pieces in two deep stages measured up to 14 % faster than 1 KB pieces in
-  // three (8192 x 28672, M = 2: 82.9 -> 72.7 us; M = 1 unchanged), FP8 the other way round
-  if (fmt == dg::FMT_BF16 && dg::shape_class(fmt, M) == 0 && steps < 3) steps = 3;
-  if (steps > row_steps) steps = row_steps;
-  while (steps > 1 && steps * x_step > 32768) --steps;
-  if (force_steps >= 1) steps = force_steps < row_steps ? force_steps : row_steps;
-  if (steps < 1) steps = 1;
-  p.steps = steps;
-  p.stage_bytes = (steps * (rows_cap * dg::kStepBytes + x_step) +
+  // The ring for activations that pass through the stages (x_step bytes of every step) or stay resident behind it
+  // (x_step = 0, resident_bytes taken from the ring's room).
+  const int pairs_bytes = p.pairs ? dg::kMeetBytes : 0;   // the SwiGLU epilogue's meeting place, behind the ring
+  auto ring = [&](int x_step, int resident_bytes, int& steps, int& stage_bytes) {
+    steps = ceil_div(32768, w_step);
+    if (steps < 2) steps = 2;
+    if (steps > 4) steps = 4;   // a tensor-copy box is at most 256 eight-byte elements (2 KB) wide
+    // BF16 rows are the longest per K: 1.5 KB pieces in two deep stages measured up to 14 % faster than 1 KB pieces
+    // in three (8192 x 28672, M = 2: 82.9 -> 72.7 us; M = 1 unchanged), FP8 the other way round
+    if (fmt == dg::FMT_BF16 && dg::shape_class(fmt, M) == 0 && steps < 3) steps = 3;
+    if (steps > row_steps) steps = row_steps;
+    while (steps > 1 && steps * x_step > 32768) --steps;
+    if (force_steps >= 1) steps = force_steps < row_steps ? force_steps : row_steps;
+    if (steps > 8) steps = 8;
+    if (steps < 1) steps = 1;
+    stage_bytes = (steps * (rows_cap * dg::kStepBytes + x_step) +
                    p.rows_per_warp * dg::scale_group_bytes(cw, steps, f.scb) + 127) & ~127;
-  // behind the ring: the SwiGLU epilogue's meeting place, then the resident activations
-  const int behind = (p.pairs ? dg::kMeetBytes : 0) + (p.x_resident ? resident_bytes : 0);
-  int stages = (smem_limit(fmt, M) - dg::kSmemHeader - behind) / p.stage_bytes;
-  if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+    int stages = (smem_limit(fmt, M) - dg::kSmemHeader - pairs_bytes - resident_bytes) / stage_bytes;
+    return stages > dg::kMaxStages ? dg::kMaxStages : stages;
+  };
+  int steps = 0, stage_bytes = 0;
+  int stages = ring(M * 64 * f.e, 0, steps, stage_bytes);
+  // Activations that are small enough stay in shared memory for the whole kernel instead of passing through the
+  // stages, unless that costs the ring its third stage: one launch's only (a batch's GEMVs each have their own).
+  const int resident_bytes = row_steps * M * 64 * f.e + ((row_steps + 15) & ~15);
+  p.x_resident = 0;
+  if (grid == 0 && dg::resident_capable(fmt, M) && resident_bytes <= dg::kResidentLimit) {
+    int steps_r = 0, stage_bytes_r = 0;
+    const int stages_r = ring(0, resident_bytes, steps_r, stage_bytes_r);
+    if (stages_r >= 3 || stages_r >= stages) {
+      p.x_resident = 1;
+      steps = steps_r; stage_bytes = stage_bytes_r; stages = stages_r;
+    }
+  }
   if (stages < 2) return false;
+  p.steps = steps;
+  p.stage_bytes = stage_bytes;
   p.stages = stages;
-  p.x_res_off = dg::kSmemHeader + stages * p.stage_bytes + (p.pairs ? dg::kMeetBytes : 0);
-  smem = dg::kSmemHeader + stages * p.stage_bytes + behind;
+  p.x_res_off = dg::kSmemHeader + stages * stage_bytes + pairs_bytes;
+  smem = p.x_res_off + (p.x_resident ? resident_bytes : 0);
   return true;
 }
 

@@ -150,7 +150,7 @@ __host__ __device__ constexpr int rows_max(int fmt, int m) {
 __host__ __device__ constexpr bool resident_capable(int fmt, int m) {
   return (fmt == FMT_FP8 || fmt == FMT_NVFP4) && shape_class(fmt, m) == 0;
 }
-constexpr int kResidentLimit = 40 * 1024;   // bytes of activations (and their flags) a kernel keeps resident at most
+constexpr int kResidentLimit = 96 * 1024;   // bytes of activations (and their flags) a kernel keeps resident at most
 // How a kernel instance advances its chains, by the activations' type too.
 //   MIXED     the mixed-precision FMA throughout: use_mixed, and every FP16-activation kernel of the formats whose
 //             decoded weights are FP16 values already (E4M3, E2M1): nothing is converted at all.

@@ -38,7 +38,7 @@ def test_plans_fit_the_device_and_do_not_depend_on_the_call(fmt, n, k):
         assert p["stages"] >= 2 and p["smem_bytes"] <= (232448 if p["ctas"] <= 148 else 115712)
         # header + ring, then (FP8 / NVFP4 at few rows) the activations that stay resident behind it
         behind = p["smem_bytes"] - (256 + p["stages"] * p["stage_bytes"])
-        assert 0 <= behind <= 40 * 1024 and (behind == 0 or fmt in ("fp8", "nvfp4"))
+        assert 0 <= behind <= 96 * 1024 + 16 and (behind == 0 or fmt in ("fp8", "nvfp4"))
         assert 1 <= p["rows_per_warp"] <= 8 and 1 <= p["steps"] <= 8
 
 

@@ -5,6 +5,7 @@
 // cudaGetLastError() after the launch, no allocation and no host synchronisation on the enqueue path.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdint>
 #include <cstdio>
@@ -142,7 +143,16 @@ int smem_limit(int fmt, int M) {
   return share == 1 ? dg::kSmemLimit : ((dg::kSmemLimit + 1024) / share - 1024) & ~127;
 }
 
-bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem, int grid = 0) {
+// Bytes of a row's activations kept resident: whole steps of [M][64 * e elements], then a flag byte per step.
+int resident_bytes_of(int fmt, int M, int nblk) {
+  const int row_steps = ceil_div(nblk, 32);
+  return row_steps * M * 64 * kFormats[fmt].e + ((row_steps + 15) & ~15);
+}
+
+// `grid` > 0: the launch is a batch's (that many CTAs whatever N; the caller sizes the ring for all its GEMVs and
+// decides about resident activations: `allow_resident` is its wish, and no stage rule is applied here).
+bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int& smem, int grid = 0,
+               bool allow_resident = true) {
   const FormatInfo f = kFormats[fmt];
   const int cw = dg::consumer_warps(fmt, M);
   const long long row_bits = (long long)K * 128 / f.e;   // 16 bytes per e elements
@@ -187,13 +197,15 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
   int steps = 0, stage_bytes = 0;
   int stages = ring(M * 64 * f.e, 0, steps, stage_bytes);
   // Activations that are small enough stay in shared memory for the whole kernel instead of passing through the
-  // stages, unless that costs the ring its third stage: one launch's only (a batch's GEMVs each have their own).
-  const int resident_bytes = row_steps * M * 64 * f.e + ((row_steps + 15) & ~15);
+  // stages, unless that costs the ring its third stage.
+  const int resident_bytes = resident_bytes_of(fmt, M, p.nblk);
   p.x_resident = 0;
-  if (grid == 0 && dg::resident_capable(fmt, M) && resident_bytes <= dg::kResidentLimit) {
+  // (a batch shares one ring and one resident area between GEMVs of different K: only the smaller ones stay resident)
+  if (allow_resident && dg::resident_capable(fmt, M) &&
+      resident_bytes <= (grid > 0 ? dg::kResidentLimit / 2 - 15 * 1024 : dg::kResidentLimit)) {
     int steps_r = 0, stage_bytes_r = 0;
     const int stages_r = ring(0, resident_bytes, steps_r, stage_bytes_r);
-    if (stages_r >= 3 || stages_r >= stages) {
+    if (grid > 0 || stages_r >= 3 || stages_r >= stages) {
       p.x_resident = 1;
       steps = steps_r; stage_bytes = stage_bytes_r; stages = stages_r;
     }
@@ -210,10 +222,10 @@ bool make_plan(int fmt, int M, int N, int K, int sms, Params& p, int& ctas, int&
 bool aligned(const void* ptr, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(ptr) % bytes == 0; }
 
 // Everything of a launch but the launch: plan, tensor maps, process-wide settings. `grid` > 0 fixes the CTA count.
-int prepare(int fmt, Params& p, int M, int& ctas, int& smem, int grid = 0) {
+int prepare(int fmt, Params& p, int M, int& ctas, int& smem, int grid = 0, bool allow_resident = true) {
   DeviceState* st = device_state();
   if (!st) return (int)cudaErrorInvalidDevice;
-  if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem, grid)) return (int)cudaErrorInvalidValue;
+  if (!make_plan(fmt, M, p.N, p.K, st->sms, p, ctas, smem, grid, allow_resident)) return (int)cudaErrorInvalidValue;
   p.status = st->status;
   // Tensor maps for the 2-D copies of full row groups; without them every row travels as a 1-D bulk copy.
   const int cw = dg::consumer_warps(fmt, M);
@@ -430,43 +442,53 @@ int dg_encode_nvfp4_batch(const DgNvfp4BatchItem* items, int count, int x_is_bf1
   if (!st) return (int)cudaErrorInvalidDevice;
   BatchHead head{};
   Params* out = reinterpret_cast<Params*>(static_cast<unsigned char*>(host_blob) + kBatchHead);
-  int stage_bytes = 0;
-  for (int g = 0; g < count; ++g) {
-    const DgNvfp4BatchItem& it = items[g];
-    Params p{};
-    if (!fill_nvfp4(p, it.x, it.ldx, x_is_bf16, it.codes, it.scales, it.blocked, it.inverse, out_kind, M, it.N, it.K))
-      return (int)cudaErrorInvalidValue;
-    if (world > 0) {
-      if (!it.peer_out) return (int)cudaErrorInvalidValue;
-      p.ldo = it.N;
-      p.world = world; p.rank = rank; p.gather_slot = slot & 1; p.gather_nowait = slot >> 1;
-      for (int q = 0; q < world; ++q) {
-        if (!it.peer_out[q] || !peer_flags[q] || !aligned(peer_flags[q], 4)) return (int)cudaErrorInvalidValue;
-        p.peer_out[q] = it.peer_out[q];
-        p.peer_flag[q] = static_cast<unsigned int*>(peer_flags[q]);
+  int stage_bytes = 0, resident_bytes = 0, stages = 0;
+  // One ring for all: the largest stage any GEMV needs, as many of them as fit. Behind the ring: room for one GEMV's
+  // parameters (kernels without producer warps keep them there), then room for the largest resident activations
+  // (every GEMV brings its own when its turn comes). If the resident ones cost the ring its third stage, once more
+  // without them.
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    stage_bytes = 0; resident_bytes = 0;
+    for (int g = 0; g < count; ++g) {
+      const DgNvfp4BatchItem& it = items[g];
+      Params p{};
+      if (!fill_nvfp4(p, it.x, it.ldx, x_is_bf16, it.codes, it.scales, it.blocked, it.inverse, out_kind, M, it.N, it.K))
+        return (int)cudaErrorInvalidValue;
+      if (world > 0) {
+        if (!it.peer_out) return (int)cudaErrorInvalidValue;
+        p.ldo = it.N;
+        p.world = world; p.rank = rank; p.gather_slot = slot & 1; p.gather_nowait = slot >> 1;
+        for (int q = 0; q < world; ++q) {
+          if (!it.peer_out[q] || !peer_flags[q] || !aligned(peer_flags[q], 4)) return (int)cudaErrorInvalidValue;
+          p.peer_out[q] = it.peer_out[q];
+          p.peer_flag[q] = static_cast<unsigned int*>(peer_flags[q]);
+        }
+        p.out = it.peer_out[rank];
+      } else {
+        if (!it.out) return (int)cudaErrorInvalidValue;
+        p.out = it.out; p.ldo = it.ldo;
       }
-      p.out = it.peer_out[rank];
-    } else {
-      if (!it.out) return (int)cudaErrorInvalidValue;
-      p.out = it.out; p.ldo = it.ldo;
+      int ctas = 0, smem = 0;
+      // one grid for all: a CTA per SM, whatever a GEMV's size (a CTA without rows of a GEMV passes it by)
+      if (const int code = prepare(dg::FMT_NVFP4, p, M, ctas, smem, st->sms * dg::ctas_per_sm(dg::FMT_NVFP4, M),
+                                   attempt == 0))
+        return code;
+      if (p.stage_bytes > stage_bytes) stage_bytes = p.stage_bytes;
+      if (p.x_resident) resident_bytes = std::max(resident_bytes, resident_bytes_of(dg::FMT_NVFP4, M, p.nblk));
+      out[g] = p;
     }
-    int ctas = 0, smem = 0;
-    // one grid for all: a CTA per SM, whatever a GEMV's size (a CTA without rows of a GEMV passes it by)
-    if (const int code = prepare(dg::FMT_NVFP4, p, M, ctas, smem, st->sms * dg::ctas_per_sm(dg::FMT_NVFP4, M))) return code;
-    if (p.stage_bytes > stage_bytes) stage_bytes = p.stage_bytes;
-    out[g] = p;
+    stages = (smem_limit(dg::FMT_NVFP4, M) - dg::kSmemHeader - (int)sizeof(Params) - resident_bytes) / stage_bytes;
+    if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+    if (resident_bytes == 0 || stages >= 3) break;
   }
-  // one ring for all: the largest stage any GEMV needs, as many of them as fit
-  // (behind the ring: room for one GEMV's parameters, which kernels without producer warps keep there)
-  int stages = (smem_limit(dg::FMT_NVFP4, M) - dg::kSmemHeader - (int)sizeof(Params)) / stage_bytes;
-  if (stages > dg::kMaxStages) stages = dg::kMaxStages;
   if (stages < 2) return (int)cudaErrorInvalidValue;
   for (int g = 0; g < count; ++g) {
     out[g].stage_bytes = stage_bytes;
     out[g].stages = stages;
+    out[g].x_res_off = dg::kSmemHeader + stages * stage_bytes + (int)sizeof(Params);
   }
   head.magic = kBatchMagic; head.count = count; head.M = M; head.ctas = st->sms * dg::ctas_per_sm(dg::FMT_NVFP4, M);
-  head.smem = dg::kSmemHeader + stages * stage_bytes + (int)sizeof(Params);
+  head.smem = dg::kSmemHeader + stages * stage_bytes + (int)sizeof(Params) + resident_bytes;
   head.threads = 32 * (dg::consumer_warps(dg::FMT_NVFP4, M) + dg::producer_warps(dg::FMT_NVFP4, M));
   head.device_blob = device_blob;
   cudaGetDevice(&head.device);

@@ -156,7 +156,7 @@ constexpr int kResidentLimit = 96 * 1024;   // bytes of activations (and their f
 //             decoded weights are FP16 values already (E4M3, E2M1): nothing is converted at all.
 //   HALF_RES  BF16 activations of a resident_capable kernel: when the activations are resident, each 512-byte step
 //             of them (64 * E elements of every activation row) is kept as FP16 if every value of it is an FP16
-//             value too (zero, or 2^-14 <= |x| <= 65504: FP16 carries BF16's 8 significant bits), and the consumers
+//             value too (|x| <= 65504, and FP16 carries BF16's 8 significant bits down to 2^-17), and the consumers
 //             run the FP16 mixed-FMA body on that step: about 2 instead of 3.5 instructions per weight at M = 1. A
 //             step with any other value (tiny, huge, infinite, NaN) stays BF16 and takes the packed FP32 body. Every
 //             product is exact either way and the additions are the same, so are the bits.
@@ -1091,15 +1091,15 @@ __device__ __forceinline__ int lane_value(int lane, int slot) {
 // ---------------------------------------------------------------------------------------------------------------
 // One tile for one consumer warp holding up to R rows (nr of them real).
 
-// Eight BF16 values as eight FP16 values, and whether that is exact for all of them with normal results (zero, or
-// 2^-14 <= |x| <= 65504; NaN and the infinities say no): the test of Arithmetic::HALF_RES.
+// Eight BF16 values as eight FP16 values, and whether each converts exactly (what FP16 holds, its subnormals
+// included: the mixed FMA takes subnormal operands exactly, checked on a B200 over every subnormal pattern; values
+// beyond 65504 become infinite, NaN compares unequal, and both say no): the test of Arithmetic::HALF_RES.
 __device__ __forceinline__ bool bf16x2_fits_half(uint32_t v, uint32_t& h) {
   const float lo = __uint_as_float(v << 16), hi = __uint_as_float(v & 0xffff0000u);
   const __half2 t = __floats2half2_rn(lo, hi);
   h = *reinterpret_cast<const uint32_t*>(&t);
-  const float alo = fabsf(lo), ahi = fabsf(hi);
-  return (alo == 0.f || (alo >= 6.103515625e-05f && alo <= 65504.f)) &&
-         (ahi == 0.f || (ahi >= 6.103515625e-05f && ahi <= 65504.f));
+  const float2 back = __half22float2(t);
+  return back.x == lo && back.y == hi;
 }
 __device__ __forceinline__ bool bf16x8_fits_half(const uint4& v, uint4& h) {
   const bool a = bf16x2_fits_half(v.x, h.x), b = bf16x2_fits_half(v.y, h.y);
@@ -1512,7 +1512,11 @@ __device__ __forceinline__ bool consume_gemv(const Params& p, const Params& maps
   bool resident = false;
   if constexpr (resident_capable(FMT, M) && !SELF) {
     resident = p.x_resident != 0;
-    if (resident) fill_resident<FMT, M, CW, Arithmetic<FMT, M, XT>::HALF_RES>(p, smem);
+    if (resident) {
+      // (a later GEMV of a batch: nobody reads the previous one's activations any more)
+      if (!first) asm volatile("bar.sync 1, %0;" ::"r"(CW * 32) : "memory");
+      fill_resident<FMT, M, CW, Arithmetic<FMT, M, XT>::HALF_RES>(p, smem);
+    }
   }
   if (first && threadIdx.x == 0) trace_stamp(p.trace, TRACE_DEP);
   int it = 0;

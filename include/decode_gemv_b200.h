@@ -203,7 +203,9 @@ DG_API int dg_hardware_decode(void);
 
 /* The launch a call with these sizes makes, for benches and tests: fmt 0 BF16, 1 FP8, 2 MXFP8, 3 NVFP4.
  * plan[0] = CTAs, [1] = rows per consumer warp and tile, [2] = 512-byte steps per ring stage, [3] = ring stages,
- * [4] = bytes per stage, [5] = dynamic shared memory bytes. Host only; returns 0, or 1 for sizes the kernels refuse. */
+ * [4] = bytes per stage, [5] = dynamic shared memory bytes (256 bytes of barriers, the ring, and, for FP8 / NVFP4 at
+ * few rows and small K, the activations, which then stay resident behind the ring for the whole kernel instead of
+ * passing through the stages). Host only; returns 0, or 1 for sizes the kernels refuse. */
 DG_API int dg_plan(int fmt, int M, int N, int K, int plan[6]);
 
 /* Reads and clears the current device's error word: bit 0 a producer wait ran out, bit 1 a consumer wait ran out,

@@ -111,16 +111,18 @@ def test_fp8_multiplies_by_the_stored_values_and_keeps_rows(mx, shape):
 @pytest.mark.parametrize("fmt", ["nvfp4", "fp8"])
 def test_activations_outside_fp16_range_keep_the_bits(fmt):
     """At few activation rows the FP8 / NVFP4 kernels hold BF16 activations as FP16 wherever a 512-byte step of them
-    fits (zero, or 2^-14 <= |x| <= 65504) and as BF16 elsewhere. Rows must not change with that choice: activations
-    with tiny, subnormal and huge values in some steps (and all of one row) against the same rows in a 16-row call,
-    whose kernel never converts them, and against the exact product."""
+    converts exactly (up to 65504, eight significant bits down to 2^-17, FP16 subnormals below) and as BF16 elsewhere.
+    Rows must not change with that choice: activations with tiny, subnormal and huge values in some steps (and all of
+    one row) against the same rows in a 16-row call, whose kernel never converts them, and against the exact
+    product."""
     n, k = 300, 4096
     host = wl.ref_nvfp4(n, k) if fmt == "nvfp4" else wl.ref_fp8(n, k, False)
     values = oc.nvfp4_values(*host) if fmt == "nvfp4" else oc.fp8_values(*host)
     t = cuda(*host)
     x = wl.activations(16, k).clone()
     x[0, 5] = 1e-30                       # far below FP16: the step stays BF16
-    x[0, 1500] = 3e-6                     # an FP16 subnormal: stays BF16 too
+    x[0, 1500] = 3e-6                     # between FP16 subnormals: stays BF16 too
+    x[0, 1800] = 2.0 ** -22               # an FP16 subnormal, exactly: fits
     x[0, 2100] = 0.0                      # zero fits
     x[1, 3000] = 70000.0                  # above FP16's largest
     x[1, 3001] = -2.0 ** -14              # the smallest normal fits

@@ -31,11 +31,7 @@ __device__ __forceinline__ float e4m3_to_f32(uint32_t byte) {
 }
 
 __device__ __forceinline__ void unpack2(dg::pk2 a, float& lo, float& hi) {
-#ifdef DG_SCALAR_PAIRS
-  lo = a.lo; hi = a.hi;
-#else
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v));
-#endif
 }
 
 // 8 codes (word c, element 2i in the low nibble of byte i) -> 8 FP32 values: (e2m1 * scale) * factor.

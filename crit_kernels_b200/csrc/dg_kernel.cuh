@@ -111,17 +111,11 @@ __host__ __device__ constexpr bool self_fed(int fmt, int m) {
 // NVFP4 7 % faster at 8192 x 8192 (M = 1); MXFP8 measured 10 % slower at M = 2 and stays.
 __host__ __device__ constexpr bool two_producers(int fmt, int m) { return (fmt == FMT_FP8 || fmt == FMT_NVFP4) && m <= 2; }
 __host__ __device__ constexpr int class2_warps(int fmt, int m) {
-#ifdef DG_C2W
-  if (fmt == DG_C2FMT && m >= DG_C2LO && m <= DG_C2HI) return DG_C2W;
-#endif
   return fmt == FMT_FP8 ? (m <= 13 ? 12 : 8)
          : fmt == FMT_BF16 ? (m <= 14 ? 12 : 8)
          : fmt == FMT_NVFP4 ? (m == 8 || m >= 11 ? 16 : 12) : 8;
 }
 __host__ __device__ constexpr int class2_rows(int fmt, int m) {
-#ifdef DG_C2W
-  if (fmt == DG_C2FMT && m >= DG_C2LO && m <= DG_C2HI) return DG_C2R;
-#endif
   return fmt == FMT_NVFP4 ? (m == 5 ? 4 : m == 8 || m >= 11 ? 2 : 3) : fmt == FMT_BF16 && m >= 12 && m <= 14 ? 3 : 4;
 }
 __host__ __device__ constexpr int consumer_warps(int fmt, int m) {
@@ -249,14 +243,6 @@ __device__ __forceinline__ uint4 ldg_nc128(const void* ptr) {   // memory nobody
 // Two FP32 values in one 64-bit register pair, the operand form of the packed fma.rn.f32x2 / mul.rn.f32x2. Operands
 // are packed once where they are produced and accumulators stay packed across the whole K loop, so that no
 // pack / unpack moves surround the FMAs (measured: almost one extra instruction per packed FMA otherwise).
-#ifdef DG_SCALAR_PAIRS   // experiment: the pair as two registers, advanced by two scalar FMAs
-struct pk2 { float lo, hi; };
-__device__ __forceinline__ pk2 pack2(float lo, float hi) { pk2 r; r.lo = lo; r.hi = hi; return r; }
-__device__ __forceinline__ pk2 pack2_bits(uint32_t lo, uint32_t hi) { return pack2(__uint_as_float(lo), __uint_as_float(hi)); }
-__device__ __forceinline__ float sum2(pk2 a) { return a.lo + a.hi; }
-__device__ __forceinline__ pk2 ffma2(pk2 a, pk2 b, pk2 c) { return pack2(fmaf(a.lo, b.lo, c.lo), fmaf(a.hi, b.hi, c.hi)); }
-__device__ __forceinline__ pk2 fmul2(pk2 a, pk2 b) { return pack2(a.lo * b.lo, a.hi * b.hi); }
-#else
 struct pk2 { unsigned long long v; };
 __device__ __forceinline__ pk2 pack2(float lo, float hi) {
   pk2 r;
@@ -283,8 +269,6 @@ __device__ __forceinline__ pk2 fmul2(pk2 a, pk2 b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d.v) : "l"(a.v), "l"(b.v));
   return d;
 }
-
-#endif
 // The same two chains as two plain FP32 registers, for the kernels that advance them with the mixed-precision FMA
 // (16-bit operands, FP32 addend and result, one rounding: fma.rn.f32.bf16 / fma.rn.f32.f16). The product of two 16-bit
 // operands is exact in FP32, so the result is bit for bit that of the FP32 FMA on the converted operands; what the
@@ -343,15 +327,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#ifdef DG_WAIT_HINT
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(DG_WAIT_HINT)
-      : "memory");
-#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -359,7 +334,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
 // Bounded wait. False when it gave up or another thread of the CTA already had: the caller leaves its loops.

@@ -42,6 +42,20 @@ def test_plans_fit_the_device_and_do_not_depend_on_the_call(fmt, n, k):
         assert 1 <= p["rows_per_warp"] <= 8 and 1 <= p["steps"] <= 8
 
 
+def test_planner_keeps_small_activations_resident():
+    """FP8 / NVFP4 at few rows: the whole [M][K] activations stay in shared memory behind the ring when they are small
+    (whole 512-byte steps of every row, plus a flag byte per step), unless that costs the ring its third stage."""
+    def behind(fmt, m, n, k):
+        p = cabi.plan(fmt, m, n, k)
+        return p["smem_bytes"] - (256 + p["stages"] * p["stage_bytes"]), p["stages"]
+    assert behind("nvfp4", 1, 8192, 8192) == (8 * 2048 + 16, 3)
+    assert behind("nvfp4", 2, 57344, 8192) == (8 * 2 * 2048 + 16, 3)
+    assert behind("fp8", 4, 28672, 8192) == (16 * 4 * 1024 + 16, 3)
+    assert behind("nvfp4", 1, 8192, 28672)[0] == 0           # 56 KB would leave two stages
+    assert behind("nvfp4", 3, 8192, 8192)[0] == 0            # a kernel whose consumers hold the rows' weights instead
+    assert behind("mxfp8", 1, 8192, 8192)[0] == 0 and behind("bf16", 1, 8192, 8192)[0] == 0
+
+
 def test_planner_refuses_what_the_kernels_refuse():
     lib = cabi.load()
     out = (ctypes.c_int * 6)()

@@ -141,8 +141,10 @@ __host__ __device__ constexpr int rows_max(int fmt, int m) {
 // Resident activations (Params::x_resident, decided by the launch plan): class 0 of FP8 / NVFP4, where the whole
 // [M][K] activations are small, keeps them in shared memory behind the ring for the whole kernel instead of copying a
 // window of them into every ring stage: the consumer warps fetch them once, while the first weights are on their way.
+// (also NVFP4's class 1, M = 3 and 4: a mixed-FMA kernel whose FP16 steps spare it the weights' conversion to BF16)
 __host__ __device__ constexpr bool resident_capable(int fmt, int m) {
-  return (fmt == FMT_FP8 || fmt == FMT_NVFP4) && shape_class(fmt, m) == 0;
+  return ((fmt == FMT_FP8 || fmt == FMT_NVFP4) && shape_class(fmt, m) == 0) ||
+         (fmt == FMT_NVFP4 && shape_class(fmt, m) == 1);
 }
 constexpr int kResidentLimit = 96 * 1024;   // bytes of activations (and their flags) a kernel keeps resident at most
 // How a kernel instance advances its chains, by the activations' type too.
@@ -152,13 +154,14 @@ constexpr int kResidentLimit = 96 * 1024;   // bytes of activations (and their f
 //             of them (64 * E elements of every activation row) is kept as FP16 if every value of it is an FP16
 //             value too (|x| <= 65504, and FP16 carries BF16's 8 significant bits down to 2^-17), and the consumers
 //             run the FP16 mixed-FMA body on that step: about 2 instead of 3.5 instructions per weight at M = 1. A
-//             step with any other value (tiny, huge, infinite, NaN) stays BF16 and takes the packed FP32 body. Every
-//             product is exact either way and the additions are the same, so are the bits.
+//             step with any other value (tiny, huge, infinite, NaN) stays BF16 and takes the kernel's other body
+//             (packed FP32, or the BF16 mixed FMA with converted weights). Every product is exact either way and the
+//             additions are the same, so are the bits.
 template <int FMT, int M, typename XT>
 struct Arithmetic {
   static constexpr bool HALF_X = std::is_same<XT, __half>::value;
   static constexpr bool MIXED = use_mixed(FMT, M) || (HALF_X && (FMT == FMT_FP8 || FMT == FMT_NVFP4));
-  static constexpr bool HALF_RES = !HALF_X && !MIXED && resident_capable(FMT, M);
+  static constexpr bool HALF_RES = !HALF_X && resident_capable(FMT, M);
 };
 
 struct Params {
@@ -1283,7 +1286,8 @@ __device__ __forceinline__ bool consume_tile(const Params& p, const Params& maps
               }
             }
             if constexpr (MIXED) {
-              body_nvfp4_mixed<M, R, XT>(wrow, woff, sc, xs, xo, acc);
+              if (HALF && as_half) body_nvfp4_mixed<M, R, __half>(wrow, woff, sc, xs, xo, acc);
+              else body_nvfp4_mixed<M, R, XT>(wrow, woff, sc, xs, xo, acc);
             } else if constexpr (HALF) {
               if (as_half) {
                 body_nvfp4_mixed<M, R, __half>(wrow, woff, sc, xs, xo, acc);

@@ -52,7 +52,8 @@ def test_planner_keeps_small_activations_resident():
     assert behind("nvfp4", 2, 57344, 8192) == (8 * 2 * 2048 + 16, 3)
     assert behind("fp8", 4, 28672, 8192) == (16 * 4 * 1024 + 16, 3)
     assert behind("nvfp4", 1, 8192, 28672)[0] == 0           # 56 KB would leave two stages
-    assert behind("nvfp4", 3, 8192, 8192)[0] == 0            # a kernel whose consumers hold the rows' weights instead
+    assert behind("nvfp4", 4, 8192, 8192)[0] == 8 * 4 * 2048 + 16
+    assert behind("fp8", 5, 8192, 8192)[0] == 0 and behind("nvfp4", 5, 8192, 8192)[0] == 0   # kernels without the mode
     assert behind("mxfp8", 1, 8192, 8192)[0] == 0 and behind("bf16", 1, 8192, 8192)[0] == 0
 
 
